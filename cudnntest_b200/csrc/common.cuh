@@ -1,0 +1,117 @@
+// Shared definitions of libwino's translation units: element types, layout strides, the problem
+// geometry derived from a wino_conv_desc, error reporting.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/wino.h"
+
+namespace wino {
+
+// ---- element types -----------------------------------------------------------------------------------
+// A float that has been rounded to the TF32 grid (10 explicit mantissa bits) when stored.
+struct tf32_t {
+    float v;
+};
+
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_float<tf32_t>(tf32_t v) { return v.v; }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ tf32_t from_float<tf32_t>(float v) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+    tf32_t t;
+    t.v = __uint_as_float(r);
+    return t;
+}
+
+// ---- layouts -----------------------------------------------------------------------------------------
+struct Strides {
+    long long n, c, h, w;
+};
+
+// element strides of an activation tensor with logical dims (N, C, H, W) stored in `layout`
+__host__ __device__ inline Strides act_strides(int layout, long long N, long long C, long long H, long long W) {
+    Strides s;
+    if (layout == WINO_NCHW) { s.n = C * H * W; s.c = H * W; s.h = W; s.w = 1; }
+    else if (layout == WINO_NHWC) { s.n = H * W * C; s.c = 1; s.h = W * C; s.w = C; }
+    else { s.n = 1; s.c = H * W * N; s.h = W * N; s.w = N; }
+    return s;
+}
+
+// element strides of the 3x3 filter tensor as (k, c, r, s); the filter layout follows the input layout
+__host__ __device__ inline Strides filter_strides(int layout, long long K, long long C) {
+    Strides s;
+    if (layout == WINO_NCHW) { s.n = C * 9; s.c = 9; s.h = 3; s.w = 1; }        // KCRS
+    else if (layout == WINO_NHWC) { s.n = 9 * C; s.c = 1; s.h = 3 * C; s.w = C; } // KRSC
+    else { s.n = 1; s.c = 9 * K; s.h = 3 * K; s.w = K; }                          // CRSK
+    return s;
+}
+
+// ---- geometry ----------------------------------------------------------------------------------------
+enum OperandKind { OP_F32 = 0, OP_TF32 = 1, OP_BF16 = 2, OP_F16 = 3 };
+
+struct Geometry {
+    int m;            // output tile side (2 or 4)
+    int a;            // input tile side m + 2
+    int oh, ow;       // conv output size before pooling
+    int ph, pw;       // stored output size (after optional pool)
+    int bny, bnx;     // tiles per image
+    int tiles_img;    // bny * bnx
+    int cp;           // V/U row length (channels padded, zero filled)
+    int kq;           // M row length
+    int operand;      // OperandKind of V and U
+    int esize_io;     // bytes per activation element
+    int esize_op;     // bytes per V/U element
+};
+
+inline int round_up(int x, int q) { return (x + q - 1) / q * q; }
+inline long long round_up_ll(long long x, long long q) { return (x + q - 1) / q * q; }
+
+// ---- errors ------------------------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int fail(int code, const char* fmt, ...);
+
+#define WINO_CUDA_CHECK(expr)                                                                     \
+    do {                                                                                          \
+        cudaError_t _e = (expr);                                                                  \
+        if (_e != cudaSuccess)                                                                    \
+            return ::wino::fail(WINO_E_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), \
+                                __FILE__, __LINE__);                                              \
+    } while (0)
+
+// ---- kernel launchers (one per translation unit) -------------------------------------------------------
+int launch_filter_transform(const wino_conv_desc& d, const Geometry& g, const void* w, void* u, cudaStream_t st);
+int launch_input_transform(const wino_conv_desc& d, const Geometry& g, const void* x, int n0, int ns, void* v,
+                           long long tp, cudaStream_t st);
+int launch_output_transform(const wino_conv_desc& d, const Geometry& g, const float* m, const float* bias,
+                            void* y, int n0, int ns, long long tp, cudaStream_t st);
+int launch_gemm_ffma(const float* v, const float* u, float* m, int batches, long long t_rows, long long tp, int k,
+                     int cp, int kq, cudaStream_t st);
+int launch_relayout(int src, int dst, int n, int c, int h, int w, int esize, const void* in, void* out,
+                    cudaStream_t st);
+int launch_maxpool(int layout, int n, int c, int h, int w, int dtype, const void* in, void* out, cudaStream_t st);
+
+}  // namespace wino

@@ -1,0 +1,124 @@
+// Exact-FP32 batched tile GEMM:  M[xi][t][k] = sum_c V[xi][t][c] * U[xi][k][c]   for xi in [0, a*a).
+//
+// Replaces GEMM_batch_256_128x128_KMKN / _MKNK (comparison/GEMM.cuh:124-255, :4-122) for the variant that
+// keeps the reference's FP32 FFMA arithmetic.  Same blocking idea (128 x BN block, 8-deep k slices,
+// 256 threads, 8 x (BN/16) register micro-tile as 4x4 quadrants, double-buffered shared memory with
+// register prefetch), written for the K-major operand buffers this library uses: both operands have the
+// contraction index contiguous, so a thread fetches one float4 along c and scatters it into a
+// [k][row] shared tile whose pitch (BM + 4) keeps the transposing stores conflict free.
+// Rows beyond the tile count / filter count are predicated (zero loads, skipped stores); the reference
+// kernel has no bounds checks and needs M, N multiples of 128.
+// Bound: FP32 FFMA issue rate (2 * a*a * T * C * K flops), not memory.
+#include "common.cuh"
+
+namespace wino {
+
+constexpr int GF_BM = 128;
+constexpr int GF_BK = 8;
+
+template <int BN>
+__global__ void __launch_bounds__(256) gemm_ffma_kernel(const float* __restrict__ V, const float* __restrict__ U,
+                                                        float* __restrict__ Mo, long long t_rows, long long tp, int K,
+                                                        int cp, int kq) {
+    constexpr int TN = BN / 16;         // columns per thread: 8 (two quadrants) or 4 (one)
+    constexpr int NQ = TN / 4;          // column quadrants
+    __shared__ __align__(16) float As[2][GF_BK][GF_BM + 4];
+    __shared__ __align__(16) float Bs[2][GF_BK][BN + 4];
+
+    const int tid = threadIdx.x;
+    const int tx = tid % 16, ty = tid / 16;
+    const long long m0 = (long long)blockIdx.x * GF_BM;
+    const int n0 = blockIdx.y * BN;
+    const int xi = blockIdx.z;
+    const float* Ap = V + (long long)xi * tp * cp;
+    const float* Bp = U + (long long)xi * K * cp;
+    float* Cp = Mo + (long long)xi * tp * kq;
+
+    // global -> register staging: one float4 along c per thread per operand
+    const int lrow = tid / 2, lk = (tid % 2) * 4;
+    const bool a_ok = (m0 + lrow) < t_rows;
+    const bool b_act = lrow < BN;
+    const bool b_ok = b_act && (n0 + lrow) < K;
+    const float* a_src = Ap + (m0 + lrow) * cp + lk;
+    const float* b_src = Bp + (long long)(n0 + lrow) * cp + lk;
+
+    float acc[8][TN];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 ra = a_ok ? *reinterpret_cast<const float4*>(a_src) : zero4;
+    float4 rb = b_ok ? *reinterpret_cast<const float4*>(b_src) : zero4;
+    As[0][lk + 0][lrow] = ra.x; As[0][lk + 1][lrow] = ra.y; As[0][lk + 2][lrow] = ra.z; As[0][lk + 3][lrow] = ra.w;
+    if (b_act) {
+        Bs[0][lk + 0][lrow] = rb.x; Bs[0][lk + 1][lrow] = rb.y; Bs[0][lk + 2][lrow] = rb.z; Bs[0][lk + 3][lrow] = rb.w;
+    }
+    __syncthreads();
+
+    const int ksteps = cp / GF_BK;  // cp is a multiple of 8
+    for (int ks = 0; ks < ksteps; ++ks) {
+        const int cur = ks & 1;
+        if (ks + 1 < ksteps) {
+            ra = a_ok ? *reinterpret_cast<const float4*>(a_src + (ks + 1) * GF_BK) : zero4;
+            rb = b_ok ? *reinterpret_cast<const float4*>(b_src + (ks + 1) * GF_BK) : zero4;
+        }
+#pragma unroll
+        for (int kk = 0; kk < GF_BK; ++kk) {
+            float a[8], b[TN];
+            const float4 a0 = *reinterpret_cast<const float4*>(&As[cur][kk][ty * 4]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&As[cur][kk][64 + ty * 4]);
+            a[0] = a0.x; a[1] = a0.y; a[2] = a0.z; a[3] = a0.w;
+            a[4] = a1.x; a[5] = a1.y; a[6] = a1.z; a[7] = a1.w;
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) {
+                const float4 bq = *reinterpret_cast<const float4*>(&Bs[cur][kk][q * (BN / 2) + tx * 4]);
+                b[q * 4 + 0] = bq.x; b[q * 4 + 1] = bq.y; b[q * 4 + 2] = bq.z; b[q * 4 + 3] = bq.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        if (ks + 1 < ksteps) {
+            const int nxt = cur ^ 1;
+            As[nxt][lk + 0][lrow] = ra.x; As[nxt][lk + 1][lrow] = ra.y; As[nxt][lk + 2][lrow] = ra.z; As[nxt][lk + 3][lrow] = ra.w;
+            if (b_act) {
+                Bs[nxt][lk + 0][lrow] = rb.x; Bs[nxt][lk + 1][lrow] = rb.y; Bs[nxt][lk + 2][lrow] = rb.z; Bs[nxt][lk + 3][lrow] = rb.w;
+            }
+        }
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const long long row = m0 + (i / 4) * 64 + ty * 4 + (i % 4);
+        if (row >= t_rows) continue;
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) {
+            const int col = n0 + q * (BN / 2) + tx * 4;
+            if (col < kq)  // kq is a multiple of 8 >= K; columns in [K, kq) hold zeros (U rows beyond K load as zero)
+                *reinterpret_cast<float4*>(Cp + row * kq + col) =
+                    make_float4(acc[i][q * 4 + 0], acc[i][q * 4 + 1], acc[i][q * 4 + 2], acc[i][q * 4 + 3]);
+        }
+    }
+}
+
+int launch_gemm_ffma(const float* v, const float* u, float* m, int batches, long long t_rows, long long tp, int k,
+                     int cp, int kq, cudaStream_t st) {
+    if (t_rows <= 0) return WINO_OK;
+    if (cp % GF_BK != 0 || kq % 4 != 0) return fail(WINO_E_BADARG, "gemm_ffma: cp=%d must be a multiple of 8, kq=%d of 4", cp, kq);
+    const unsigned mb = (unsigned)((t_rows + GF_BM - 1) / GF_BM);
+    if (k <= 64) {
+        dim3 grid(mb, (unsigned)((k + 63) / 64), (unsigned)batches);
+        gemm_ffma_kernel<64><<<grid, 256, 0, st>>>(v, u, m, t_rows, tp, k, cp, kq);
+    } else {
+        dim3 grid(mb, (unsigned)((k + 127) / 128), (unsigned)batches);
+        gemm_ffma_kernel<128><<<grid, 256, 0, st>>>(v, u, m, t_rows, tp, k, cp, kq);
+    }
+    WINO_CUDA_CHECK(cudaGetLastError());
+    return WINO_OK;
+}
+
+}  // namespace wino

@@ -1,0 +1,18 @@
+// Tensor-core batched tile GEMM (tcgen05 / TMEM / TMA), declarations.
+#pragma once
+
+#include "common.cuh"
+
+namespace wino {
+
+// M[xi][t][k] = sum_c V[xi][t][c] * U[xi][k][c], xi in [0, batches); operand = OP_TF32 / OP_BF16 / OP_F16.
+// V: [batches][tp][cp], U: [batches][k][cp] (cp elements per row, row pitch a multiple of 16 bytes),
+// M: [batches][tp][kq] float.  Rows t >= t_rows are neither read nor written.
+int launch_gemm_tc(int operand, const void* v, const void* u, float* m, int batches, long long t_rows, long long tp,
+                   int k, int cp, int kq, cudaStream_t st);
+
+// Device-side status word of the tensor-core kernels: 0 = fine, otherwise the code of the first bounded
+// wait that gave up.  Reading it synchronises the device and clears it.
+int read_and_clear_tc_status(int* status);
+
+}  // namespace wino

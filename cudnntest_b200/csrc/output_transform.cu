@@ -1,0 +1,226 @@
+// Output transform Y = A^T M A fused with bias, ReLU, optional 2x2 max-pool and the scatter into
+// NCHW / NHWC / CHWN.
+//
+// Replaces wino_invers_nchw_suitFor128_3 / _nhwc_suitFor128 / _chwn_suitFor128_2
+// (comparison/wrapedConv_NCHW.cuh:1034-1114, wrapedConv_NHWC.cuh:376-428, wrapedConv_CHWN.cuh:379-431)
+// and the separate bias / ReLU / pool passes the reference runs afterwards
+// (netTest/cudnn_test_0124/VGG_Batched/Network.h:456-519, CHWN_support.cuh:85-120, :198-270, :480-527).
+//
+// Every layout reads the same product buffer M[xi][tile][Kq] (filters contiguous, 128 B per warp load)
+// with one thread per (tile, filter); the layouts differ in the scatter:
+//   * NHWC: the filter index is the contiguous output dimension, so the thread stores directly;
+//   * NCHW: TX adjacent tiles x 32 filters are staged in shared memory and written as row segments
+//     contiguous along w;
+//   * CHWN: one tile position x 8 images x 32 filters are staged and written contiguous along n.
+// HBM bound: reads a*a*T*K floats, writes N*K*OH*OW elements (a quarter of that with the pool).
+#include "common.cuh"
+#include "wino_math.cuh"
+
+namespace wino {
+
+struct OTArgs {
+    const float* m;
+    const float* bias;
+    void* y;
+    int K;
+    int oh, ow;   // conv output size
+    int ph, pw;   // stored output size
+    int n0, ns;
+    int bny, bnx;
+    int kq;
+    long long tp;
+    int relu, pool;
+    Strides sy;   // strides of y (dims N, K, ph, pw)
+};
+
+constexpr int OT_KB = 32;
+constexpr int OT_TX = 8;
+constexpr int OT_NB = 8;
+
+// Loads the a*a products of (tile t, filter k), applies A^T . A, bias, ReLU and (POOL) the 2x2 max.
+// res[p][q] holds the MO x MO stored outputs of the tile, MO = M or M/2.
+template <int A, bool POOL>
+__device__ __forceinline__ void tile_outputs(const OTArgs& a, long long t, int k,
+                                             float (&res)[POOL ? (A - 2) / 2 : (A - 2)][POOL ? (A - 2) / 2 : (A - 2)]) {
+    constexpr int M = A - 2;
+    float mm[A][A], y[M][M];
+    const long long plane = a.tp * a.kq;
+    const float* src = a.m + t * a.kq + k;
+#pragma unroll
+    for (int i = 0; i < A; ++i)
+#pragma unroll
+        for (int j = 0; j < A; ++j) mm[i][j] = __ldg(src + (long long)(i * A + j) * plane);
+    output_tile_transform<A>(mm, y);
+    const float b = a.bias ? __ldg(a.bias + k) : 0.f;
+#pragma unroll
+    for (int p = 0; p < M; ++p)
+#pragma unroll
+        for (int q = 0; q < M; ++q) {
+            float v = y[p][q] + b;
+            if (a.relu) v = fmaxf(v, 0.f);
+            y[p][q] = v;
+        }
+    if constexpr (POOL) {
+#pragma unroll
+        for (int p = 0; p < M / 2; ++p)
+#pragma unroll
+            for (int q = 0; q < M / 2; ++q)
+                res[p][q] = fmaxf(fmaxf(y[2 * p][2 * q], y[2 * p][2 * q + 1]), fmaxf(y[2 * p + 1][2 * q], y[2 * p + 1][2 * q + 1]));
+    } else {
+#pragma unroll
+        for (int p = 0; p < M; ++p)
+#pragma unroll
+            for (int q = 0; q < M; ++q) res[p][q] = y[p][q];
+    }
+}
+
+// NHWC destination: direct store, lanes along k
+template <int A, bool POOL, typename TOut>
+__global__ void __launch_bounds__(256) output_transform_direct(OTArgs a, long long T) {
+    constexpr int MO = POOL ? (A - 2) / 2 : (A - 2);
+    const int kchunks = (a.K + OT_KB - 1) / OT_KB;
+    const long long item = (long long)blockIdx.x * 256 + threadIdx.x;
+    const int k = (int)(item % (kchunks * OT_KB));
+    const long long t = item / (kchunks * OT_KB);
+    if (t >= T || k >= a.K) return;
+    float res[MO][MO];
+    tile_outputs<A, POOL>(a, t, k, res);
+    const int tiles_img = a.bny * a.bnx;
+    const int n = a.n0 + (int)(t / tiles_img);
+    const int rem = (int)(t % tiles_img);
+    const int by = rem / a.bnx, bx = rem % a.bnx;
+    TOut* __restrict__ y = (TOut*)a.y + (long long)n * a.sy.n + (long long)k * a.sy.c;
+#pragma unroll
+    for (int p = 0; p < MO; ++p) {
+        const int oy = by * MO + p;
+        if (oy >= a.ph) continue;
+#pragma unroll
+        for (int q = 0; q < MO; ++q) {
+            const int ox = bx * MO + q;
+            if (ox < a.pw) y[oy * a.sy.h + ox * a.sy.w] = from_float<TOut>(res[p][q]);
+        }
+    }
+}
+
+// NCHW destination: stage TX tiles x 32 filters, store rows contiguous along w
+template <int A, bool POOL, typename TOut>
+__global__ void __launch_bounds__(256) output_transform_strip(OTArgs a) {
+    constexpr int MO = POOL ? (A - 2) / 2 : (A - 2);
+    constexpr int COLS = MO * OT_TX;
+    constexpr int PITCH = OT_KB + 1;
+    __shared__ float stage[MO * COLS * PITCH];
+
+    const int kchunks = (a.K + OT_KB - 1) / OT_KB;
+    const int k0 = (blockIdx.x % kchunks) * OT_KB;
+    const int bx0 = (blockIdx.x / kchunks) * OT_TX;
+    const int by = blockIdx.y;
+    const int n = a.n0 + blockIdx.z;
+
+    {
+        const int k_l = threadIdx.x % OT_KB, tl = threadIdx.x / OT_KB;
+        const int bx = bx0 + tl, k = k0 + k_l;
+        if (bx < a.bnx && k < a.K) {
+            float res[MO][MO];
+            const long long t = ((long long)blockIdx.z * a.bny + by) * a.bnx + bx;
+            tile_outputs<A, POOL>(a, t, k, res);
+#pragma unroll
+            for (int p = 0; p < MO; ++p)
+#pragma unroll
+                for (int q = 0; q < MO; ++q) stage[(p * COLS + tl * MO + q) * PITCH + k_l] = res[p][q];
+        }
+    }
+    __syncthreads();
+    TOut* __restrict__ y = (TOut*)a.y + (long long)n * a.sy.n;
+    for (int idx = threadIdx.x; idx < MO * COLS * OT_KB; idx += 256) {
+        const int col = idx % COLS;
+        const int rk = idx / COLS;
+        const int k_l = rk % OT_KB;
+        const int p = rk / OT_KB;
+        const int oy = by * MO + p, ox = bx0 * MO + col, k = k0 + k_l;
+        if (oy < a.ph && ox < a.pw && k < a.K)
+            y[(long long)k * a.sy.c + oy * a.sy.h + ox * a.sy.w] = from_float<TOut>(stage[(p * COLS + col) * PITCH + k_l]);
+    }
+}
+
+// CHWN destination: stage 8 images x 32 filters of one tile position, store contiguous along n
+template <int A, bool POOL, typename TOut>
+__global__ void __launch_bounds__(256) output_transform_batch(OTArgs a) {
+    constexpr int MO = POOL ? (A - 2) / 2 : (A - 2);
+    constexpr int PITCH = OT_KB + 4;
+    __shared__ float stage[MO * MO * OT_NB * PITCH];
+
+    const int kchunks = (a.K + OT_KB - 1) / OT_KB;
+    const int k0 = (blockIdx.x % kchunks) * OT_KB;
+    const int nb0 = (blockIdx.x / kchunks) * OT_NB;
+    const int bx = blockIdx.y, by = blockIdx.z;
+
+    {
+        const int k_l = threadIdx.x % OT_KB, n_l = threadIdx.x / OT_KB;
+        const int k = k0 + k_l;
+        if (nb0 + n_l < a.ns && k < a.K) {
+            float res[MO][MO];
+            const long long t = ((long long)(nb0 + n_l) * a.bny + by) * a.bnx + bx;
+            tile_outputs<A, POOL>(a, t, k, res);
+#pragma unroll
+            for (int p = 0; p < MO; ++p)
+#pragma unroll
+                for (int q = 0; q < MO; ++q) stage[((p * MO + q) * OT_NB + n_l) * PITCH + k_l] = res[p][q];
+        }
+    }
+    __syncthreads();
+    TOut* __restrict__ y = (TOut*)a.y;
+    for (int idx = threadIdx.x; idx < MO * MO * OT_NB * OT_KB; idx += 256) {
+        const int n_l = idx % OT_NB;
+        const int rk = idx / OT_NB;
+        const int k_l = rk % OT_KB;
+        const int pq = rk / OT_KB;
+        const int oy = by * MO + pq / MO, ox = bx * MO + pq % MO, k = k0 + k_l;
+        if (oy < a.ph && ox < a.pw && k < a.K && nb0 + n_l < a.ns)
+            y[(long long)(a.n0 + nb0 + n_l) * a.sy.n + (long long)k * a.sy.c + oy * a.sy.h + ox * a.sy.w] =
+                from_float<TOut>(stage[(pq * OT_NB + n_l) * PITCH + k_l]);
+    }
+}
+
+template <int A, bool POOL, typename TOut>
+static int run(const wino_conv_desc& d, const Geometry& g, const OTArgs& a, cudaStream_t st) {
+    static_assert(OT_TX * OT_KB == 256 && OT_NB * OT_KB == 256, "one work item per thread");
+    const int kchunks = (d.k + OT_KB - 1) / OT_KB;
+    if (d.layout_out == WINO_NHWC) {
+        const long long T = (long long)a.ns * g.tiles_img;
+        const long long items = T * kchunks * OT_KB;
+        output_transform_direct<A, POOL, TOut><<<(unsigned)((items + 255) / 256), 256, 0, st>>>(a, T);
+    } else if (d.layout_out == WINO_NCHW) {
+        dim3 grid((unsigned)(((g.bnx + OT_TX - 1) / OT_TX) * kchunks), (unsigned)g.bny, (unsigned)a.ns);
+        output_transform_strip<A, POOL, TOut><<<grid, 256, 0, st>>>(a);
+    } else {
+        dim3 grid((unsigned)(((a.ns + OT_NB - 1) / OT_NB) * kchunks), (unsigned)g.bnx, (unsigned)g.bny);
+        output_transform_batch<A, POOL, TOut><<<grid, 256, 0, st>>>(a);
+    }
+    WINO_CUDA_CHECK(cudaGetLastError());
+    return WINO_OK;
+}
+
+template <int A>
+static int dispatch(const wino_conv_desc& d, const Geometry& g, const OTArgs& a, cudaStream_t st) {
+    const bool bf16 = d.dtype == WINO_BF16;
+    if (d.pool2x2)
+        return bf16 ? run<A, true, __nv_bfloat16>(d, g, a, st) : run<A, true, float>(d, g, a, st);
+    return bf16 ? run<A, false, __nv_bfloat16>(d, g, a, st) : run<A, false, float>(d, g, a, st);
+}
+
+int launch_output_transform(const wino_conv_desc& d, const Geometry& g, const float* m, const float* bias,
+                            void* y, int n0, int ns, long long tp, cudaStream_t st) {
+    if (ns <= 0) return WINO_OK;
+    if (ns > 65535 || g.bny > 65535 || g.bnx > 65535)
+        return fail(WINO_E_UNSUPPORTED, "output transform: slab of %d images / %dx%d tiles exceeds the grid limits", ns,
+                    g.bny, g.bnx);
+    OTArgs a;
+    a.m = m; a.bias = d.has_bias ? bias : nullptr; a.y = y; a.K = d.k;
+    a.oh = g.oh; a.ow = g.ow; a.ph = g.ph; a.pw = g.pw;
+    a.n0 = n0; a.ns = ns; a.bny = g.bny; a.bnx = g.bnx; a.kq = g.kq; a.tp = tp;
+    a.relu = d.relu; a.pool = d.pool2x2;
+    a.sy = act_strides(d.layout_out, d.n, d.k, g.ph, g.pw);
+    return g.a == 6 ? dispatch<6>(d, g, a, st) : dispatch<4>(d, g, a, st);
+}
+
+}  // namespace wino

@@ -1,0 +1,123 @@
+// The three Winograd transforms as fully unrolled register arithmetic, for F(4x4,3x3) (A = 6) and
+// F(2x2,3x3) (A = 4).  Matrices of F(4x4,3x3) are the reference's:
+//   B^T  comparison/wrapedConv_NCHW.cuh:836-855     G  :881-898     A^T  :1084-1101
+// with G applied as multiplications by constants, not divisions.  F(2x2,3x3) uses the Lavin-Gray form.
+#pragma once
+
+namespace wino {
+
+// 1-D input transform t = B^T d
+template <int A>
+__device__ __forceinline__ void bt_1d(const float (&d)[A], float (&t)[A]);
+
+template <>
+__device__ __forceinline__ void bt_1d<6>(const float (&d)[6], float (&t)[6]) {
+    t[0] = 4.f * d[0] - 5.f * d[2] + d[4];
+    t[1] = -4.f * (d[1] + d[2]) + d[3] + d[4];
+    t[2] = 4.f * (d[1] - d[2]) - d[3] + d[4];
+    t[3] = -2.f * d[1] - d[2] + 2.f * d[3] + d[4];
+    t[4] = 2.f * d[1] - d[2] - 2.f * d[3] + d[4];
+    t[5] = 4.f * d[1] - 5.f * d[3] + d[5];
+}
+template <>
+__device__ __forceinline__ void bt_1d<4>(const float (&d)[4], float (&t)[4]) {
+    t[0] = d[0] - d[2];
+    t[1] = d[1] + d[2];
+    t[2] = d[2] - d[1];
+    t[3] = d[1] - d[3];
+}
+
+// V = B^T d B for one A x A patch held in registers (row major d[r][s]); result v[i][j]
+template <int A>
+__device__ __forceinline__ void input_tile_transform(const float (&d)[A][A], float (&v)[A][A]) {
+    float tmp[A][A];  // tmp[r][j] = sum_s d[r][s] B[s][j]
+#pragma unroll
+    for (int r = 0; r < A; ++r) bt_1d<A>(d[r], tmp[r]);
+#pragma unroll
+    for (int j = 0; j < A; ++j) {
+        float col[A], out[A];
+#pragma unroll
+        for (int r = 0; r < A; ++r) col[r] = tmp[r][j];
+        bt_1d<A>(col, out);
+#pragma unroll
+        for (int i = 0; i < A; ++i) v[i][j] = out[i];
+    }
+}
+
+// 1-D filter transform u = G g
+template <int A>
+__device__ __forceinline__ void g_1d(const float (&g)[3], float (&u)[A]);
+
+template <>
+__device__ __forceinline__ void g_1d<6>(const float (&g)[3], float (&u)[6]) {
+    const float s = g[0] + g[2];
+    u[0] = 0.25f * g[0];
+    u[1] = (-1.f / 6.f) * (s + g[1]);
+    u[2] = (-1.f / 6.f) * (s - g[1]);
+    const float q = (1.f / 24.f) * g[0] + (1.f / 6.f) * g[2];
+    u[3] = q + (1.f / 12.f) * g[1];
+    u[4] = q - (1.f / 12.f) * g[1];
+    u[5] = g[2];
+}
+template <>
+__device__ __forceinline__ void g_1d<4>(const float (&g)[3], float (&u)[4]) {
+    const float s = g[0] + g[2];
+    u[0] = g[0];
+    u[1] = 0.5f * (s + g[1]);
+    u[2] = 0.5f * (s - g[1]);
+    u[3] = g[2];
+}
+
+template <int A>
+__device__ __forceinline__ void filter_tile_transform(const float (&g)[3][3], float (&u)[A][A]) {
+    float tmp[3][A];  // tmp[r][j] = sum_s g[r][s] G[j][s]
+#pragma unroll
+    for (int r = 0; r < 3; ++r) g_1d<A>(g[r], tmp[r]);
+#pragma unroll
+    for (int j = 0; j < A; ++j) {
+        float col[3], out[A];
+#pragma unroll
+        for (int r = 0; r < 3; ++r) col[r] = tmp[r][j];
+        g_1d<A>(col, out);
+#pragma unroll
+        for (int i = 0; i < A; ++i) u[i][j] = out[i];
+    }
+}
+
+// 1-D output transform y = A^T m
+template <int A>
+__device__ __forceinline__ void at_1d(const float (&m)[A], float (&y)[A - 2]);
+
+template <>
+__device__ __forceinline__ void at_1d<6>(const float (&m)[6], float (&y)[4]) {
+    const float s12 = m[1] + m[2], d12 = m[1] - m[2];
+    const float s34 = m[3] + m[4], d34 = m[3] - m[4];
+    y[0] = m[0] + s12 + s34;
+    y[1] = d12 + 2.f * d34;
+    y[2] = s12 + 4.f * s34;
+    y[3] = d12 + 8.f * d34 + m[5];
+}
+template <>
+__device__ __forceinline__ void at_1d<4>(const float (&m)[4], float (&y)[2]) {
+    y[0] = m[0] + m[1] + m[2];
+    y[1] = m[1] - m[2] - m[3];
+}
+
+// Y = A^T M A for one A x A tile of products (row major mm[i][j]); result y[p][q]
+template <int A>
+__device__ __forceinline__ void output_tile_transform(const float (&mm)[A][A], float (&y)[A - 2][A - 2]) {
+    float tmp[A][A - 2];  // tmp[i][q] = sum_j mm[i][j] A[j][q]
+#pragma unroll
+    for (int i = 0; i < A; ++i) at_1d<A>(mm[i], tmp[i]);
+#pragma unroll
+    for (int q = 0; q < A - 2; ++q) {
+        float col[A], out[A - 2];
+#pragma unroll
+        for (int i = 0; i < A; ++i) col[i] = tmp[i][q];
+        at_1d<A>(col, out);
+#pragma unroll
+        for (int p = 0; p < A - 2; ++p) y[p][q] = out[p];
+    }
+}
+
+}  // namespace wino

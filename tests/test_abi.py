@@ -1,0 +1,79 @@
+"""CPU-side checks of the C ABI: the library loads, exports what include/wino.h declares, validates
+descriptors and sizes buffers — no compute call needs a GPU here."""
+import ctypes
+import math
+
+import pytest
+
+import cudnntest_b200 as cb
+
+
+@pytest.fixture(scope="module")
+def L():
+    return cb.lib()
+
+
+def test_exports_every_declared_symbol(L):
+    names = cb.declared_symbols()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(L, n), n
+    assert L.wino_version() >= 100
+
+
+def test_descriptor_validation(L):
+    good = cb.make_desc(8, 64, 56, 56, 64, layout="NCHW")
+    assert L.wino_conv_workspace_bytes(ctypes.byref(good)) > 0
+    for field, value in (("pad", 2), ("wino", 3), ("dtype", 7), ("layout_in", 5), ("c", 0), ("k", -1), ("operand", 9)):
+        d = cb.make_desc(8, 64, 56, 56, 64, layout="NCHW", dtype="bf16")
+        setattr(d, field, value)
+        assert L.wino_conv_workspace_bytes(ctypes.byref(d)) == 0, field
+        assert L.wino_last_error_string()
+    assert L.wino_conv_workspace_bytes(None) == 0
+
+
+@pytest.mark.parametrize("shape", [(8, 64, 56, 56, 64), (64, 256, 56, 56, 256), (1, 3, 224, 224, 64), (128, 512, 14, 14, 512)])
+@pytest.mark.parametrize("dtype", ["fp32", "tf32", "bf16"])
+@pytest.mark.parametrize("m", [2, 4])
+def test_buffer_sizes(L, shape, dtype, m):
+    n, c, h, w, k = shape
+    d = cb.make_desc(n, c, h, w, k, dtype=dtype, wino=m)
+    dp = ctypes.byref(d)
+    a = m + 2
+    cp, kq = L.wino_stage_cp(dp), L.wino_stage_kq(dp)
+    assert cp == math.ceil(c / 8) * 8 and kq == math.ceil(k / 8) * 8
+    es = 2 if dtype == "bf16" else 4
+    assert L.wino_filter_bytes(dp) == a * a * k * cp * es
+    tiles = math.ceil(h / m) * math.ceil(w / m)
+    assert L.wino_stage_tile_rows(dp, 3) == math.ceil(3 * tiles / 128) * 128
+    # the default slab keeps V + M of one pass within the L2 budget unless a single image exceeds it
+    ws = L.wino_conv_workspace_bytes(dp)
+    per_image = a * a * tiles * (cp * es + kq * 4)
+    assert ws >= per_image
+    assert ws <= max(48 << 20, per_image) + a * a * 128 * (cp * es + kq * 4) + 4096
+    # an explicit slab of the whole batch needs the whole-batch buffers
+    d.slab_images = n
+    assert L.wino_conv_workspace_bytes(dp) >= n * per_image
+
+
+def test_legacy_workspaces_cover_the_slabs(L):
+    """The reference callers' minimum buffer sizes hold this library's V, U, M for any slab."""
+    for (n, h, c, k) in ((1, 224, 3, 64), (8, 56, 64, 64), (64, 28, 512, 512), (3, 14, 20, 130)):
+        vf, uf, mf = cb.legacy_workspace_floats(n, h, c, k, 1)
+        d = cb.make_desc(n, c, h, h, k, dtype="fp32", wino=4)
+        dp = ctypes.byref(d)
+        cp, kq, tp = L.wino_stage_cp(dp), L.wino_stage_kq(dp), L.wino_stage_tile_rows(dp, n)
+        assert 36 * tp * cp <= vf and 36 * k * cp <= uf and 36 * tp * kq <= mf
+
+
+def test_no_cpu_fallback(L):
+    """Without a CUDA device every compute entry point fails loudly with WINO_E_CUDA."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    d = cb.make_desc(1, 8, 8, 8, 8)
+    buf = (ctypes.c_float * 16)()
+    rc = L.wino_filter_transform(ctypes.byref(d), buf, buf, None)
+    assert rc == cb._lib.E_CUDA
+    assert b"no CPU path" in L.wino_last_error_string()
+    assert L.wino_device_status() == cb._lib.E_CUDA

@@ -1,0 +1,103 @@
+"""GPU parity of the tensor-core variants (tcgen05 tile GEMM): TF32 and BF16 storage with BF16/FP16 operands.
+
+Tolerance: relative L2 error <= 5e-3 against the double-accumulating direct-convolution oracle on the
+FP32 seeded tensors (the bar BASELINE.json's north_star states for TF32 and BF16).  The tile GEMM alone
+is compared with a GEMM of the same rounded operands, which it must match to accumulation-order noise.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+
+import oracle
+from util import LAYOUTS, make_inputs, maxrel, rel_l2, run_conv, to_dev
+
+pytestmark = pytest.mark.gpu
+TOL_L2 = 5e-3
+
+
+@pytest.fixture(scope="module")
+def cb():
+    import torch
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    import cudnntest_b200
+    cudnntest_b200.lib()
+    return cudnntest_b200
+
+
+@pytest.mark.parametrize("dtype,operand,kind", [("tf32", 0, "tf32"), ("bf16", 1, "bf16"), ("bf16", 2, "f16")])
+@pytest.mark.parametrize("shape", [(200, 64, 64), (130, 24, 40), (1000, 256, 256), (128, 8, 200)])
+def test_tile_gemm_alone(cb, dtype, operand, kind, shape):
+    """wino_stage_gemm on random operands of the right format vs float64 GEMM of the same values."""
+    import torch
+    t, c, k = shape
+    # a 1-row "image" with t tiles: n = t, h = w = 2 gives one tile per image for m = 4
+    d = cb.make_desc(t, c, 2, 2, k, layout="NHWC", dtype=dtype, operand=operand, wino=4)
+    L = cb.lib()
+    dp = ctypes.byref(d)
+    cp, kq, tp = L.wino_stage_cp(dp), L.wino_stage_kq(dp), L.wino_stage_tile_rows(dp, t)
+    rng = np.random.default_rng(t + c + k)
+    v = np.zeros((36, tp, cp), dtype=np.float32)
+    u = np.zeros((36, k, cp), dtype=np.float32)
+    v[:, :t, :c] = oracle.round_to(rng.uniform(-4, 4, (36, t, c)).astype(np.float32), kind)
+    u[:, :, :c] = oracle.round_to((rng.standard_normal((36, k, c)) * 0.05).astype(np.float32), kind)
+    v[:, t:, :] = np.nan      # rows past the tile count must never be read into valid outputs
+    tdt = {"tf32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[kind]
+    vd, ud = to_dev(v, tdt), to_dev(u, tdt)
+    mm = torch.full((36, tp, kq), float("nan"), device="cuda")
+    P = lambda z: ctypes.c_void_p(z.data_ptr())
+    cb._lib.check(L.wino_stage_gemm(dp, P(vd), P(ud), P(mm), t, None))
+    cb.device_status()
+    ref = oracle.tile_gemm(v[:, :t, :c], u[:, :, :c])
+    got = mm.cpu().numpy()
+    assert np.isfinite(got[:, :t, :k]).all()
+    assert maxrel(got[:, :t, :k], ref) <= 2e-6
+    assert np.all(got[:, :t, k:] == 0)
+
+
+@pytest.mark.parametrize("layout", LAYOUTS)
+@pytest.mark.parametrize("dtype,wino,operand", [("tf32", 4, 0), ("tf32", 2, 0), ("bf16", 4, 0), ("bf16", 2, 0), ("bf16", 4, 1)])
+def test_conv_reduced_precision(cb, layout, dtype, wino, operand):
+    n, c, h, w, k = 4, 64, 28, 28, 96
+    x, wt, b = make_inputs(n, c, h, w, k, seed=31)
+    y = run_conv(x, wt, b, layout, dtype=dtype, wino=wino, relu=True, operand=operand)
+    ref = oracle.conv_f64(x, wt, bias=b, relu=True)
+    err = rel_l2(y, ref)
+    if dtype == "bf16" and wino == 4 and operand == 1:
+        # pure-BF16 operands with F(4x4,3x3) are outside the tolerance by construction; they must still
+        # agree with the CPU emulation of the same rounding points
+        emu = oracle.winograd_conv(x, wt, 1, 4, bias=b, relu=True, storage="bf16", operand="bf16")
+        assert rel_l2(y, emu) <= 5e-3
+        assert err <= 5e-2
+    else:
+        assert err <= TOL_L2, err
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 16, 16, 64), (3, 40, 9, 13, 72), (1, 512, 14, 14, 512)])
+def test_conv_bf16_ragged(cb, shape):
+    n, c, h, w, k = shape
+    x, wt, b = make_inputs(n, c, h, w, k, seed=sum(shape))
+    for layout in LAYOUTS:
+        y = run_conv(x, wt, b, layout, dtype="bf16", relu=True, pool=(h % 2 == 0))
+        ref = oracle.conv_f64(x, wt, bias=b, relu=True, pool=(h % 2 == 0))
+        assert rel_l2(y, ref) <= TOL_L2
+
+
+def test_full_size_config1_bf16(cb):
+    """BASELINE config 1 at full size, BF16 NHWC: first two images vs the oracle, slab-size invariance."""
+    n, c, h, k = 64, 256, 56, 256
+    x, wt, b = make_inputs(n, c, h, h, k, seed=0xC0DE0010)
+    y = run_conv(x, wt, b, "NHWC", dtype="bf16", relu=True)
+    y2 = run_conv(x, wt, b, "NHWC", dtype="bf16", relu=True, slab_images=7)
+    assert np.array_equal(y, y2)
+    ref = oracle.conv_f64(x[:2], wt, bias=b, relu=True)
+    assert rel_l2(y[:2], ref) <= TOL_L2
+
+
+def test_full_size_config3_bf16_nchw(cb):
+    """BASELINE config 3: N=128, C=K=512, 14x14, BF16, NCHW, bias+ReLU; four images vs the oracle."""
+    n, c, h, k = 128, 512, 14, 512
+    x, wt, b = make_inputs(n, c, h, h, k, seed=0xC0DE0030)
+    y = run_conv(x, wt, b, "NCHW", dtype="bf16", relu=True)
+    ref = oracle.conv_f64(x[:4], wt, bias=b, relu=True)
+    assert rel_l2(y[:4], ref) <= TOL_L2
