@@ -1,0 +1,322 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: the VGG-16 convolution stack (13 Winograd 3x3 convolutions with fused
+bias + ReLU, 2x2 max-pool fused at the five block ends) on synthetic data.
+
+    python bench.py --gpus N --steps K --warmup W [--dtype bf16|tf32|fp32] [--layout NHWC|NCHW|CHWN]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...      (N > 1)
+    python bench.py --impl reference ...        the CPU arm: the direct-convolution oracle on the host cores
+
+One step = one forward pass of the stack over one batch.  The batch dimension shards across GPUs with
+no data-path collective (every rank runs its own images with replicated weights); per-GPU batch is fixed
+at --batch (default 256), so the job is weak-scaled and `value` is the aggregate images/s.
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "vgg16_conv_stack_images_per_s"
+UNIT = "images/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "tf32", "fp32"])
+    ap.add_argument("--layout", default="NHWC", choices=["NHWC", "NCHW", "CHWN"])
+    ap.add_argument("--batch", type=int, default=256, help="images per GPU per step")
+    ap.add_argument("--wino", type=int, default=0, choices=[0, 2, 4])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the cpu_baseline sample")
+    return ap.parse_args()
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "tflops_burst": p["bf16_tflops"], "tflops_sustained": p["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ---- clocks -------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1])); power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm),
+                "power_w_max": max(power)}
+
+
+# ---- CPU arm --------------------------------------------------------------------------------------------
+def cpu_stack_images_per_s(layout, images, repeats=1):
+    """Times the oracle's float32 direct convolution (all host threads) over the 13-layer stack."""
+    import numpy as np
+    import oracle
+    from cudnntest_b200.vgg import VGG16_CONV
+    rng = np.random.default_rng(0xC0DE0040)
+    x = oracle.to_layout(rng.uniform(-1, 1, (images, 3, 224, 224)).astype(np.float32), layout)
+    ws, bs = [], []
+    for (c, k, s, pool) in VGG16_CONV:
+        ws.append(oracle.filter_to_layout((rng.standard_normal((k, c, 3, 3)) * np.sqrt(2.0 / (9 * c))).astype(np.float32), layout))
+        bs.append((rng.standard_normal(k) * 0.01).astype(np.float32))
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        cur = x
+        for (c, k, s, pool), w, b in zip(VGG16_CONV, ws, bs):
+            cur = oracle.conv_f32(cur, w, bias=b, relu=True, pool=pool, layout=layout)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return images / best, best
+
+
+def cpu_baseline(layout, target_seconds):
+    import oracle
+    rate, dt = cpu_stack_images_per_s(layout, 1)
+    images = int(max(1, min(64, target_seconds / max(dt, 1e-3))))
+    if images > 1:
+        rate, dt = cpu_stack_images_per_s(layout, images)
+    return {"value": rate, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+            "sample": "%d image(s) through all 13 layers, float32 direct convolution (oracle/wino_ref.cpp, OpenMP), "
+                      "%.1f s" % (images, dt)}
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    import oracle
+    oracle.build()
+    config = workload_config(args)
+    rate, dt = cpu_stack_images_per_s(args.layout, 1)       # sizing probe
+    images = int(max(1, min(16, 20.0 / max(dt, 1e-3) / max(args.steps + args.warmup, 1))))
+    for _ in range(args.warmup):
+        cpu_stack_images_per_s(args.layout, images)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_stack_images_per_s(args.layout, images)
+    total = time.perf_counter() - t0
+    value = images * args.steps / total
+    sample = "each step = %d image(s) through all 13 layers on the host cores (bounded sample of the %d-image batch)" % (
+        images, args.batch)
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference has no C/C++ CPU convolution (its ground truth is a numpy triple loop); this arm times the "
+                "C++ restatement of that loop, oracle/wino_ref.cpp"}))
+
+
+def workload_config(args):
+    return {"workload": "VGG-16 conv stack forward: 13 3x3 pad-1 convs 64,64|128,128|256x3|512x3|512x3, input 3x224x224, "
+                        "bias+ReLU after each conv, 2x2 max-pool after each block",
+            "per_gpu_batch": args.batch, "global_batch": args.batch * args.gpus, "layout": args.layout,
+            "parallelism": "batch-sharded x%d, no collective" % args.gpus,
+            "init": "He-normal weights, bias N(0,0.01), input U[-1,1], seeded",
+            "l2": "256 MiB buffer rewritten between timed iterations"}
+
+
+# ---- GPU arm --------------------------------------------------------------------------------------------
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import cudnntest_b200 as cb
+    from cudnntest_b200 import vgg
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (libwino has no CPU path)")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    L = cb.lib()
+    peaks = load_peaks()
+
+    stack = vgg.VGG16ConvStack(args.batch, layout=args.layout, dtype=args.dtype, wino=args.wino, seed=0xC0DE0040 + rank)
+    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    x_host = (torch.rand(stack.in_shape, generator=gen) * 2 - 1).to(stack.io_dtype).pin_memory()
+    x_dev = x_host.cuda(non_blocking=True)
+    y_host = torch.empty(stack.out_shape, dtype=stack.io_dtype).pin_memory()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(step_fn, steps):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record(stream)
+        for _ in range(steps):
+            flush.zero_()
+            step_fn()
+        stop.record(stream)
+        torch.cuda.synchronize()
+        barrier()
+        ms = start.elapsed_time(stop)
+        if dist is not None:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def step_resident():
+        stack(x_dev)
+
+    def step_e2e():
+        xd = x_host.cuda(non_blocking=True)
+        y = stack(xd)
+        y_host.copy_(y, non_blocking=True)
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    cb.device_status()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = L.wino_launch_count()
+    ms = timed(step_resident, args.steps)
+    launches = L.wino_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    cb.device_status()
+
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    cb.device_status()
+
+    # per-stage device time of one more step, each kernel bracketed by events on its stream
+    import ctypes
+    L.wino_profile_enable(1)
+    step_resident()
+    stage_ms = (ctypes.c_float * 4)()
+    stage_n = (ctypes.c_longlong * 4)()
+    L.wino_profile_read(stage_ms, stage_n)
+    L.wino_profile_enable(0)
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    images = args.batch * world
+    value = images * args.steps / (ms * 1e-3)
+    e2e_value = images * args.steps / (ms_e2e * 1e-3)
+    esize = 2 if args.dtype == "bf16" else 4
+    wino = args.wino or 4
+    a = wino + 2
+    gemm_flops = vgg.winograd_gemm_flops_per_image(wino) * args.batch
+    names = ("input_transform", "tile_gemm", "output_transform", "filter_transform")
+    stage = {n: {"ms": float(stage_ms[i]), "launches": int(stage_n[i])} for i, n in enumerate(names)}
+    # algorithmic bytes of the transform stages for the whole step (per-GPU batch)
+    in_bytes = sum((c * s * s * esize + a * a * -(-s // wino) ** 2 * (-(-c // 8) * 8) * esize) for (c, k, s, p) in vgg.VGG16_CONV) * args.batch
+    out_bytes = sum((a * a * -(-s // wino) ** 2 * k * 4 + k * (s // 2 if p else s) ** 2 * esize) for (c, k, s, p) in vgg.VGG16_CONV) * args.batch
+    dominant = max(range(3), key=lambda i: stage_ms[i])
+    if dominant == 1:
+        peak = peaks["tflops_sustained"] * (0.5 if args.dtype == "tf32" else 1.0)
+        achieved = gemm_flops / (stage_ms[1] * 1e-3) / 1e12
+        roofline = {"kernel": "gemm_tc_kernel" if args.dtype != "fp32" else "gemm_ffma_kernel", "bound": "tensor",
+                    "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                    "peak_source": peaks["source"] + " (sustained bf16 cuBLAS; halved for tf32)"}
+    else:
+        b = in_bytes if dominant == 0 else out_bytes
+        achieved = b / (stage_ms[dominant] * 1e-3) / 1e9
+        roofline = {"kernel": names[dominant], "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                    "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]}
+    roofline["per_launch_ms"] = stage[names[dominant]]["ms"] / max(stage[names[dominant]]["launches"], 1)
+    roofline["stage_ms_per_step"] = {n: round(stage[n]["ms"], 4) for n in names[:3]}
+    roofline["stage_launches_per_step"] = {n: stage[n]["launches"] for n in names[:3]}
+
+    out = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": args.dtype, "data": "synthetic", "config": workload_config(args),
+        "tflops_direct_equivalent": vgg.direct_flops_per_image() * value / 1e12,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * x_host.element_size() * world,
+                "d2h_bytes_per_step": y_host.numel() * y_host.element_size() * world, "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        import oracle
+        oracle.build()
+        out["cpu_baseline"] = cpu_baseline(args.layout, args.cpu_seconds)
+    print(json.dumps(out))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("--gpus %d needs torchrun with %d ranks (one process per GPU)" % (args.gpus, args.gpus))
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

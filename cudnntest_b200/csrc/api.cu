@@ -9,9 +9,12 @@
 //     before it is evicted, and the buffers are reused by the next slab, so the two largest
 //     intermediates of the pipeline do not round-trip through HBM;
 //   * everything is asynchronous on the caller's stream; only wino_wraped_conv synchronises.
+#include <atomic>
 #include <cstdarg>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "gemm_tc.cuh"
@@ -33,6 +36,38 @@ int fail(int code, const char* fmt, ...) {
     vsnprintf(g_err, sizeof(g_err), fmt, ap);
     va_end(ap);
     return code;
+}
+
+// ---- measurement hooks ---------------------------------------------------------------------------------
+static std::atomic<long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+namespace {
+struct ProfRecord {
+    cudaEvent_t start, stop;
+    int stage;
+};
+std::mutex g_prof_mutex;
+bool g_prof_on = false;
+std::vector<ProfRecord> g_prof;
+}  // namespace
+
+ProfScope::ProfScope(int stage, cudaStream_t s) : slot(-1), st(s) {
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    if (!g_prof_on) return;
+    ProfRecord r;
+    r.stage = stage;
+    if (cudaEventCreate(&r.start) != cudaSuccess) return;
+    if (cudaEventCreate(&r.stop) != cudaSuccess) { cudaEventDestroy(r.start); return; }
+    cudaEventRecord(r.start, st);
+    g_prof.push_back(r);
+    slot = (int)g_prof.size() - 1;
+}
+
+ProfScope::~ProfScope() {
+    if (slot < 0) return;
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    if (slot < (int)g_prof.size()) cudaEventRecord(g_prof[slot].stop, st);
 }
 
 static bool layout_ok(int l) { return l == WINO_NCHW || l == WINO_NHWC || l == WINO_CHWN; }
@@ -134,6 +169,34 @@ extern "C" {
 const char* wino_last_error_string(void) { return g_err; }
 
 int wino_version(void) { return 100; }
+
+long long wino_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int wino_profile_enable(int on) {
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    g_prof_on = on != 0;
+    return WINO_OK;
+}
+
+int wino_profile_read(float stage_ms[4], long long stage_launches[4]) {
+    if (!stage_ms || !stage_launches) return fail(WINO_E_BADARG, "profile read: NULL pointer");
+    for (int i = 0; i < 4; ++i) { stage_ms[i] = 0.f; stage_launches[i] = 0; }
+    int rc = check_device();
+    if (rc) return rc;
+    WINO_CUDA_CHECK(cudaDeviceSynchronize());
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    for (ProfRecord& r : g_prof) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, r.start, r.stop) == cudaSuccess && r.stage >= 0 && r.stage < 4) {
+            stage_ms[r.stage] += ms;
+            stage_launches[r.stage] += 1;
+        }
+        cudaEventDestroy(r.start);
+        cudaEventDestroy(r.stop);
+    }
+    g_prof.clear();
+    return WINO_OK;
+}
 
 int wino_device_status(void) {
     int rc = check_device();

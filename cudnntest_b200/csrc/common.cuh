@@ -102,6 +102,17 @@ int fail(int code, const char* fmt, ...);
                                 __FILE__, __LINE__);                                              \
     } while (0)
 
+// ---- measurement hooks -----------------------------------------------------------------------------------
+void count_launch();
+enum Stage { STAGE_INPUT = 0, STAGE_GEMM = 1, STAGE_OUTPUT = 2, STAGE_FILTER = 3 };
+// brackets one kernel launch with CUDA events when profiling is enabled
+struct ProfScope {
+    ProfScope(int stage, cudaStream_t st);
+    ~ProfScope();
+    int slot;
+    cudaStream_t st;
+};
+
 // ---- kernel launchers (one per translation unit) -------------------------------------------------------
 int launch_filter_transform(const wino_conv_desc& d, const Geometry& g, const void* w, void* u, cudaStream_t st);
 int launch_input_transform(const wino_conv_desc& d, const Geometry& g, const void* x, int n0, int ns, void* v,

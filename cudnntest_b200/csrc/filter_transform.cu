@@ -44,6 +44,8 @@ static int run(const wino_conv_desc& d, const Geometry& g, const void* w, void* 
     const long long total = (long long)d.k * g.cp;
     const int threads = 256;
     const long long blocks = (total + threads - 1) / threads;
+    ProfScope prof(STAGE_FILTER, st);
+    count_launch();
     filter_transform_kernel<A, TIn, TOp><<<(unsigned)blocks, threads, 0, st>>>(
         (const TIn*)w, (TOp*)u, d.k, d.c, g.cp, filter_strides(d.layout_in, d.k, d.c));
     WINO_CUDA_CHECK(cudaGetLastError());

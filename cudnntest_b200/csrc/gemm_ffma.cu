@@ -110,6 +110,8 @@ int launch_gemm_ffma(const float* v, const float* u, float* m, int batches, long
     if (t_rows <= 0) return WINO_OK;
     if (cp % GF_BK != 0 || kq % 4 != 0) return fail(WINO_E_BADARG, "gemm_ffma: cp=%d must be a multiple of 8, kq=%d of 4", cp, kq);
     const unsigned mb = (unsigned)((t_rows + GF_BM - 1) / GF_BM);
+    ProfScope prof(STAGE_GEMM, st);
+    count_launch();
     if (k <= 64) {
         dim3 grid(mb, (unsigned)((k + 63) / 64), (unsigned)batches);
         gemm_ffma_kernel<64><<<grid, 256, 0, st>>>(v, u, m, t_rows, tp, k, cp, kq);

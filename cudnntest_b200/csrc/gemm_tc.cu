@@ -385,6 +385,8 @@ int run(const CUtensorMap& tm_v, const CUtensorMap& tm_u, const TcParams& p, cud
     WINO_CUDA_CHECK(attr_err);
     const long long total = (long long)p.batches * p.mblocks * p.nblocks;
     const int grid = (int)(total < sm_count() ? total : sm_count());
+    ProfScope prof(STAGE_GEMM, st);
+    count_launch();
     gemm_tc_kernel<BN, TF32, STAGES><<<grid, TC_THREADS, L::TOTAL, st>>>(tm_v, tm_u, p);
     WINO_CUDA_CHECK(cudaGetLastError());
     return WINO_OK;

@@ -140,6 +140,8 @@ template <int A, typename TIn, typename TOp>
 static int run(const wino_conv_desc& d, const Geometry& g, const ITArgs& a, cudaStream_t st) {
     static_assert(IT_TX * IT_CB == 256 && IT_NB * IT_CB == 256, "one work item per thread");
     const int cchunks = (g.cp + IT_CB - 1) / IT_CB;
+    ProfScope prof(STAGE_INPUT, st);
+    count_launch();
     if (d.layout_in == WINO_CHWN) {
         dim3 grid((unsigned)(((a.ns + IT_NB - 1) / IT_NB) * cchunks), (unsigned)g.bnx, (unsigned)g.bny);
         input_transform_batch<A, TIn, TOp><<<grid, 256, 0, st>>>(a);

@@ -185,6 +185,8 @@ template <int A, bool POOL, typename TOut>
 static int run(const wino_conv_desc& d, const Geometry& g, const OTArgs& a, cudaStream_t st) {
     static_assert(OT_TX * OT_KB == 256 && OT_NB * OT_KB == 256, "one work item per thread");
     const int kchunks = (d.k + OT_KB - 1) / OT_KB;
+    ProfScope prof(STAGE_OUTPUT, st);
+    count_launch();
     if (d.layout_out == WINO_NHWC) {
         const long long T = (long long)a.ns * g.tiles_img;
         const long long items = T * kchunks * OT_KB;

@@ -43,6 +43,7 @@ static int run_transpose(const void* in, void* out, long long B, long long R, lo
     if (B * qtiles > 0x7fffffffLL || rtiles > 65535 || R > 0x7fffffffLL || Q > 0x7fffffffLL)
         return fail(WINO_E_UNSUPPORTED, "relayout: tensor too large for one launch");
     dim3 grid((unsigned)(B * qtiles), (unsigned)rtiles);
+    count_launch();
     transpose_batched_kernel<T><<<grid, 256, 0, st>>>((const T*)in, (T*)out, (int)R, (int)Q, (int)qtiles, sb_in, sr_in,
                                                        sb_out, sq_out);
     WINO_CUDA_CHECK(cudaGetLastError());
@@ -92,6 +93,7 @@ int launch_maxpool(int layout, int n, int c, int h, int w, int dtype, const void
     if (total == 0) return WINO_OK;
     const long long blocks = (total + 255) / 256;
     if (blocks > 0x7fffffffLL) return fail(WINO_E_UNSUPPORTED, "maxpool: tensor too large for one launch");
+    count_launch();
     if (dtype == WINO_BF16)
         maxpool_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, layout,
                                                                           n, c, h, w, total);

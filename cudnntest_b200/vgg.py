@@ -1,0 +1,94 @@
+"""VGG-16 convolution stack on the Winograd engine: 13 3x3 pad-1 convolutions, bias + ReLU after each,
+2x2 max-pool after each block — the conv part of the reference's network path
+(netTest/cudnn_test_0124/VGG_Batched/Network.h:603-669, layer table vggCUDNN.cu:154-180).
+
+Where the reference runs conv, bias, ReLU and pool as four to seven kernels per layer, each layer here
+is one ``wino_conv_forward`` call whose output transform applies bias, ReLU and (at block ends) the
+pool.  Weights are random He-initialised (the pretrained ``vggData/conv*.bin`` are not shipped with the
+reference); activations ping-pong between two buffers and all layers share one scratch buffer.
+"""
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+from .conv import WinoConv, act_shape, make_desc
+
+# (input channels, filters, input side, pool after)
+VGG16_CONV = [
+    (3, 64, 224, False), (64, 64, 224, True),
+    (64, 128, 112, False), (128, 128, 112, True),
+    (128, 256, 56, False), (256, 256, 56, False), (256, 256, 56, True),
+    (256, 512, 28, False), (512, 512, 28, False), (512, 512, 28, True),
+    (512, 512, 14, False), (512, 512, 14, False), (512, 512, 14, True),
+]
+
+
+def direct_flops_per_image(layers=VGG16_CONV):
+    """Direct-convolution-equivalent FLOPs of the stack for one image: sum of 2*K*C*H*W*9."""
+    return sum(2 * k * c * s * s * 9 for (c, k, s, _) in layers)
+
+
+def algorithmic_bytes_per_image(esize, layers=VGG16_CONV):
+    """Sum over layers of (input + output) activation bytes for one image (filters are batch independent)."""
+    total = 0
+    for (c, k, s, pool) in layers:
+        o = s // 2 if pool else s
+        total += (c * s * s + k * o * o) * esize
+    return total
+
+
+def winograd_gemm_flops_per_image(wino=4, layers=VGG16_CONV):
+    """FLOPs of the tile GEMMs: 2 * a^2 * tiles * C * K, tiles = ceil(H/m)^2 (unpadded)."""
+    a = wino + 2
+    return sum(2 * a * a * math.ceil(s / wino) ** 2 * c * k for (c, k, s, _) in layers)
+
+
+class VGG16ConvStack:
+    """The 13-layer stack for a fixed batch size, layout and dtype."""
+
+    def __init__(self, batch, layout="NHWC", dtype="bf16", wino=0, seed=0xC0DE0040, device="cuda", layers=VGG16_CONV,
+                 slab_images=0):
+        self.batch, self.layout, self.dtype = batch, layout, dtype
+        self.layers = list(layers)
+        self.device = torch.device(device)
+        self.io_dtype = torch.bfloat16 if dtype == "bf16" else torch.float32
+        ws_bytes = 0
+        for (c, k, s, pool) in self.layers:
+            d = make_desc(batch, c, s, s, k, layout, None, dtype, 1, wino, True, True, pool, 0, slab_images)
+            ws_bytes = max(ws_bytes, _lib.lib().wino_conv_workspace_bytes(ctypes.byref(d)))
+        self.workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=self.device)
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        self.convs, self.weights, self.biases = [], [], []
+        max_act = 0
+        for (c, k, s, pool) in self.layers:
+            conv = WinoConv(batch, c, s, s, k, layout=layout, dtype=dtype, wino=wino, relu=True, bias=True, pool=pool,
+                            slab_images=slab_images, device=device, workspace=self.workspace)
+            w_kcrs = torch.randn((k, c, 3, 3), generator=gen) * math.sqrt(2.0 / (9 * c))
+            b = torch.randn(k, generator=gen) * 0.01
+            perm = {0: (0, 1, 2, 3), 1: (0, 2, 3, 1), 2: (1, 2, 3, 0)}[conv.desc.layout_in]
+            w_l = w_kcrs.permute(perm).contiguous().to(self.io_dtype).to(self.device)
+            b = b.to(self.device)
+            conv.set_filter(w_l, b)
+            self.convs.append(conv)
+            self.weights.append(w_kcrs)
+            self.biases.append(b)
+            o = s // 2 if pool else s
+            max_act = max(max_act, batch * k * o * o)
+        self.act = [torch.empty(max_act, dtype=self.io_dtype, device=self.device) for _ in range(2)]
+        c0, _, s0, _ = self.layers[0]
+        self.in_shape = act_shape(layout, batch, c0, s0, s0)
+        self.out_shape = self.convs[-1].out_shape
+        self.launches_per_forward = None
+
+    def forward(self, x):
+        """x: input batch in `layout` (device tensor of in_shape).  Returns a view into an internal buffer."""
+        cur = x
+        for i, conv in enumerate(self.convs):
+            out = self.act[i % 2][: math.prod(conv.out_shape)].view(conv.out_shape)
+            conv(cur, out=out)
+            cur = out
+        return cur
+
+    __call__ = forward

@@ -114,6 +114,17 @@ int wino_layout_convert(int layout_src, int layout_dst, int n, int c, int h, int
 int wino_maxpool2x2(int layout, int n, int c, int h, int w, int dtype, const void* in, void* out,
                     wino_stream_t stream);
 
+/* ---- measurement hooks ----------------------------------------------------------------------------
+ * wino_launch_count: kernels launched by this process through the library so far.
+ * wino_profile_enable(1): from now on every kernel launched by wino_conv_forward / wino_filter_transform is
+ * bracketed by a pair of CUDA events on its own stream (takes the role of the commented-out five-event
+ * per-stage breakdown of comparison/wrapedConv_NCHW.cuh:88-138).  wino_profile_read synchronises the
+ * device, adds up the elapsed milliseconds and launches per stage since the last read (index 0 input
+ * transform, 1 tile GEMM, 2 output transform, 3 filter transform) and clears the record. */
+long long wino_launch_count(void);
+int wino_profile_enable(int on);
+int wino_profile_read(float stage_ms[4], long long stage_launches[4]);
+
 /* ---- stage-level entry points (tests, profiling) --------------------------------------------------
  * Buffers for a slab of `ns` images starting at image n0 (T = ns*bny*bnx tiles, bny = ceil((h+2p-2)/m)):
  *   V[xi][Tp][Cp]  xi = a*i + j (a = m+2), tile t = (n-n0)*bny*bnx + by*bnx + bx, Cp = c rounded up to
