@@ -269,8 +269,11 @@ def run_ours(args, rank, world, local_rank):
     names = ("input_transform", "tile_gemm", "output_transform", "filter_transform")
     stage = {n: {"ms": float(stage_ms[i]), "launches": int(stage_n[i])} for i, n in enumerate(names)}
     # algorithmic bytes of the transform stages for the whole step (per-GPU batch)
-    in_bytes = sum((c * s * s * esize + a * a * -(-s // wino) ** 2 * (-(-c // 8) * 8) * esize) for (c, k, s, p) in vgg.VGG16_CONV) * args.batch
-    out_bytes = sum((a * a * -(-s // wino) ** 2 * k * 4 + k * (s // 2 if p else s) ** 2 * esize) for (c, k, s, p) in vgg.VGG16_CONV) * args.batch
+    ceil = lambda p_, q_: -(-p_ // q_)
+    in_bytes = sum(c * s * s * esize + a * a * ceil(s, wino) ** 2 * ceil(c, 8) * 8 * esize
+                   for (c, k, s, p) in vgg.VGG16_CONV) * args.batch
+    out_bytes = sum(a * a * ceil(s, wino) ** 2 * k * 4 + k * (s // 2 if p else s) ** 2 * esize
+                    for (c, k, s, p) in vgg.VGG16_CONV) * args.batch
     dominant = max(range(3), key=lambda i: stage_ms[i])
     if dominant == 1:
         peak = peaks["tflops_sustained"] * (0.5 if args.dtype == "tf32" else 1.0)

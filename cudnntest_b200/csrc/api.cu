@@ -74,7 +74,7 @@ static bool layout_ok(int l) { return l == WINO_NCHW || l == WINO_NHWC || l == W
 
 // Validates a descriptor and derives the tiling.  Mirrors wrapedConv_NCHW.cuh:346-362 (inside_beta,
 // blockn, M/N/K sizes) with rectangular images and without the 128/128 padding of M and N.
-static int make_geometry(const wino_conv_desc* d, Geometry* g) {
+int make_geometry(const wino_conv_desc* d, Geometry* g) {
     if (!d) return fail(WINO_E_BADARG, "descriptor is NULL");
     if (!layout_ok(d->layout_in) || !layout_ok(d->layout_out))
         return fail(WINO_E_BADARG, "bad layout code (in %d, out %d)", d->layout_in, d->layout_out);
@@ -91,7 +91,7 @@ static int make_geometry(const wino_conv_desc* d, Geometry* g) {
         case WINO_TF32: g->operand = OP_TF32; g->esize_io = 4; g->esize_op = 4; break;
         case WINO_BF16:
             g->esize_io = 2; g->esize_op = 2;
-            if (d->operand == WINO_OPERAND_AUTO) g->operand = g->m == 4 ? OP_F16 : OP_BF16;
+            if (d->operand == WINO_OPERAND_AUTO) g->operand = OP_F16;
             else if (d->operand == WINO_OPERAND_BF16) g->operand = OP_BF16;
             else if (d->operand == WINO_OPERAND_F16) g->operand = OP_F16;
             else return fail(WINO_E_BADARG, "bad operand code %d", d->operand);
@@ -120,7 +120,7 @@ static long long slab_budget_bytes() {
     return budget;
 }
 
-static long long per_image_bytes(const Geometry& g) {
+long long per_image_bytes(const Geometry& g) {
     return (long long)g.a * g.a * g.tiles_img * ((long long)g.cp * g.esize_op + (long long)g.kq * 4);
 }
 
@@ -134,23 +134,23 @@ static int slab_images(const wino_conv_desc& d, const Geometry& g) {
     return (int)ns;
 }
 
-static long long tile_rows(const Geometry& g, int ns) { return round_up_ll((long long)ns * g.tiles_img, 128); }
+long long tile_rows(const Geometry& g, int ns) { return round_up_ll((long long)ns * g.tiles_img, 128); }
 
-static size_t v_bytes(const Geometry& g, long long tp) {
+size_t v_bytes(const Geometry& g, long long tp) {
     return (size_t)round_up_ll((long long)g.a * g.a * tp * g.cp * g.esize_op, 1024);
 }
-static size_t m_bytes(const Geometry& g, long long tp) {
+size_t m_bytes(const Geometry& g, long long tp) {
     return (size_t)round_up_ll((long long)g.a * g.a * tp * g.kq * 4, 1024);
 }
 
-static int run_gemm(const Geometry& g, const void* v, const void* u, float* m, int k, long long t_rows, long long tp,
+int run_gemm(const Geometry& g, const void* v, const void* u, float* m, int k, long long t_rows, long long tp,
                     cudaStream_t st) {
     if (g.operand == OP_F32)
         return launch_gemm_ffma((const float*)v, (const float*)u, m, g.a * g.a, t_rows, tp, k, g.cp, g.kq, st);
     return launch_gemm_tc(g.operand, v, u, m, g.a * g.a, t_rows, tp, k, g.cp, g.kq, st);
 }
 
-static int check_device() {
+int check_device() {
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) {

@@ -102,6 +102,16 @@ int fail(int code, const char* fmt, ...);
                                 __FILE__, __LINE__);                                              \
     } while (0)
 
+// ---- host helpers shared by the entry points (defined in api.cu) --------------------------------------
+int make_geometry(const wino_conv_desc* d, Geometry* g);   // validates the descriptor, derives the tiling
+long long per_image_bytes(const Geometry& g);              // V + M bytes one image contributes to a slab
+long long tile_rows(const Geometry& g, int ns);            // rows per V/M plane for a slab of ns images
+size_t v_bytes(const Geometry& g, long long tp);
+size_t m_bytes(const Geometry& g, long long tp);
+int run_gemm(const Geometry& g, const void* v, const void* u, float* m, int k, long long t_rows, long long tp,
+             cudaStream_t st);
+int check_device();
+
 // ---- measurement hooks -----------------------------------------------------------------------------------
 void count_launch();
 enum Stage { STAGE_INPUT = 0, STAGE_GEMM = 1, STAGE_OUTPUT = 2, STAGE_FILTER = 3 };

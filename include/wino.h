@@ -53,8 +53,8 @@ typedef struct wino_conv_desc {
     int layout_in, layout_out; /* WINO_NCHW / WINO_NHWC / WINO_CHWN; may differ (convLayoutTrans_*) */
     int n, c, h, w, k, pad;    /* batch, input channels, height, width, filters, zero padding        */
     int dtype;                 /* WINO_FP32 / WINO_TF32 / WINO_BF16                                  */
-    int operand;               /* WINO_BF16 only: format of the transformed operands; AUTO = F16 for
-                                  F(4x4,3x3), BF16 for F(2x2,3x3)                                     */
+    int operand;               /* WINO_BF16 only: format of the transformed operands; AUTO = F16 (FP16
+                                  operands keep both tile sizes inside the 5e-3 tolerance)          */
     int wino;                  /* output tile size m of F(m x m, 3x3): 2 or 4; 0 = 4                  */
     int relu, has_bias, pool2x2; /* epilogue fused into the output transform: y = pool(relu(conv+b)) */
     int slab_images;           /* images transformed per pass; 0 = sized so a pass stays L2 resident */
