@@ -75,6 +75,10 @@ def lib():
     L.wino_conv_workspace_bytes.argtypes = [P]
     L.wino_filter_transform.argtypes = [P, V, V, V]
     L.wino_conv_forward.argtypes = [P, V, V, V, V, V, SZ, V]
+    L.wino_static_scratch_bytes.restype = SZ
+    L.wino_static_scratch_bytes.argtypes = []
+    L.wino_conv_forward_static.argtypes = [P, V, V, V, V, V]
+    L.wino_conv_forward_static.restype = I
     L.wino_wraped_conv.argtypes = [I, I, I, I, ctypes.POINTER(I), I, I, V, V, V, V, V, ctypes.POINTER(V)]
     L.wino_layout_convert.argtypes = [I, I, I, I, I, I, I, V, V, V]
     L.wino_maxpool2x2.argtypes = [I, I, I, I, I, I, V, V, V]

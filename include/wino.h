@@ -91,6 +91,21 @@ int wino_filter_transform(const wino_conv_desc* d, const void* w, void* u, wino_
 int wino_conv_forward(const wino_conv_desc* d, const void* x, const void* u, const float* bias, void* y,
                       void* workspace, size_t workspace_bytes, wino_stream_t stream);
 
+/* Convolution forward for callers that cannot allocate device memory.  No counterpart in the reference
+ * (its drivers cudaMalloc whatever they need, comparison/layoutCompare.cu:120-126).  Same result as
+ * wino_conv_forward, but the slab scratch (V and M) is a fixed array of WINO_STATIC_SCRATCH_BYTES that is
+ * part of the library image on every GPU that loads it, so the caller passes tensors only and the call
+ * performs no cudaMalloc / cudaFree / allocating library routine.  Meant for hosts whose memory pool is
+ * frozen after start-up or that run under a foreign allocator or a no-synchronisation rule.
+ * The first call on each device resolves the array's device address: make it before any stream capture.
+ * A problem whose one-image slab exceeds the array fails with WINO_E_WORKSPACE.  All calls on a device
+ * share the array (it keeps the last call's contents; nothing in it has to start at zero): calls that
+ * overlap on the GPU race, so keep them on one stream or otherwise serialised. */
+#define WINO_STATIC_SCRATCH_BYTES (64u << 20)
+size_t wino_static_scratch_bytes(void);
+int wino_conv_forward_static(const wino_conv_desc* d, const void* x, const void* u, const float* bias, void* y,
+                             wino_stream_t stream);
+
 /* The reference's wrapper signature, C-callable.  Replaces wrapedConv_<L> (comparison/wrapedConv_NCHW.cuh:8,
  * wrapedConv_NHWC.cuh:8, wrapedConv_CHWN.cuh:8), layoutManager (comparison/DataLayoutTrans.cuh:594-651)
  * and convLayoutTrans_<S>_to_<D> (DataLayoutTrans.cuh:9,101,192,309,418,502).  FP32 path, F(4x4,3x3),

@@ -1,0 +1,77 @@
+"""wino_conv_forward_static: the forward call for hosts that may not allocate device memory.
+
+A serving process that froze its memory pool at start-up, or a plugin living under another framework's
+allocator, cannot hand libwino a freshly cudaMalloc'ed scratch buffer.  This entry point keeps the slab
+scratch in an array built into the library, so the test checks exactly what such a caller relies on:
+the result equals wino_conv_forward's on the same tensors, a second call right after the first (reusing
+the array with the previous call's contents still in it) is just as good, and a problem too large for the
+array is refused with a message instead of overrunning it.
+
+This file sorts last on purpose: a run that stops at the first failure has already run everything else.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+
+import oracle
+from util import make_inputs, maxrel, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_both(cb, n, c, h, w, k, layout, dtype, seed):
+    import torch
+    L = cb.lib()
+    tdt = torch.bfloat16 if dtype == "bf16" else torch.float32
+    x, wt, b = make_inputs(n, c, h, w, k, seed=seed)
+    conv = cb.WinoConv(n, c, h, w, k, layout=layout, dtype=dtype, relu=True, bias=True)
+    bd = to_dev(b)
+    conv.set_filter(to_dev(oracle.filter_to_layout(wt, layout), tdt), bd)
+    xd = to_dev(oracle.to_layout(x, layout), tdt)
+    y_ref = conv(xd)
+    cb.device_status()
+    outs = []
+    for _ in range(2):                                   # two calls in a row share the built-in scratch
+        y = torch.full(conv.out_shape, float("nan"), dtype=tdt, device="cuda")
+        rc = L.wino_conv_forward_static(ctypes.byref(conv.desc), xd.data_ptr(), conv.u.data_ptr(), bd.data_ptr(),
+                                        y.data_ptr(), None)
+        assert rc == 0, L.wino_last_error_string()
+        cb.device_status()
+        outs.append(y.float().cpu().numpy())
+    return y_ref.float().cpu().numpy(), outs
+
+
+@pytest.mark.parametrize("layout,dtype,shape", [
+    ("NHWC", "fp32", (5, 16, 20, 20, 24)),
+    ("NCHW", "fp32", (3, 8, 13, 9, 40)),
+    ("NHWC", "bf16", (40, 64, 56, 56, 64)),      # 40 images x 2.7 MB of V+M each: more than one slab of the 64 MiB array
+    ("CHWN", "bf16", (9, 32, 14, 14, 96)),
+])
+def test_static_scratch_matches_caller_scratch(layout, dtype, shape):
+    import torch
+    assert torch.cuda.is_available()
+    import cudnntest_b200 as cb
+    n, c, h, w, k = shape
+    ref, outs = _run_both(cb, n, c, h, w, k, layout, dtype, seed=sum(shape))
+    tol = 1e-4 if dtype == "fp32" else 5e-3             # the tolerances of the FP32 and BF16 parity tests
+    for y in outs:
+        assert np.isfinite(y).all()
+        assert maxrel(y, ref.astype(np.float64)) <= tol
+    assert np.array_equal(outs[0], outs[1])
+
+
+def test_static_scratch_rejects_oversized_problem():
+    import torch
+    assert torch.cuda.is_available()
+    import cudnntest_b200 as cb
+    L = cb.lib()
+    assert L.wino_static_scratch_bytes() == 64 << 20
+    # one 224x224 image with 128 -> 128 channels needs ~115 MB of V + M in FP32: more than the array holds
+    d = cb.make_desc(1, 128, 224, 224, 128, layout="NHWC", dtype="fp32")
+    dummy = torch.zeros(16, device="cuda")
+    rc = L.wino_conv_forward_static(ctypes.byref(d), dummy.data_ptr(), dummy.data_ptr(), None, dummy.data_ptr(), None)
+    assert rc == cb._lib.E_WORKSPACE
+    msg = L.wino_last_error_string().decode()
+    assert "built-in array holds" in msg and "67108864" in msg
+    assert L.wino_device_status() == 0
