@@ -18,6 +18,7 @@
 
 #include "common.cuh"
 #include "gemm_tc.cuh"
+#include "ptx.cuh"
 
 namespace wino {
 
@@ -115,7 +116,7 @@ static long long slab_budget_bytes() {
     static long long budget = [] {
         const char* e = getenv("WINO_SLAB_BYTES");
         long long v = e ? atoll(e) : 0;
-        return v > 0 ? v : (48LL << 20);
+        return v > 0 ? v : (2048LL << 20);
     }();
     return budget;
 }
@@ -202,8 +203,8 @@ int wino_device_status(void) {
     int rc = check_device();
     if (rc) return rc;
     int s = 0;
-    if ((rc = read_and_clear_tc_status(&s))) return rc;
-    if (s != 0) return fail(WINO_E_TIMEOUT, "a tensor-core GEMM CTA gave up waiting (wait code %d: 1 ring slot free, 2 ring slot filled, 3 accumulator drained, 4 accumulator ready)", s);
+    if ((rc = read_and_clear_status(&s))) return rc;
+    if (s != 0) return fail(WINO_E_TIMEOUT, "a CTA gave up a bounded wait (code %d: tile GEMM 1 ring slot free, 2 ring slot filled, 3 accumulator drained, 4 accumulator ready; 5 input-transform patch load)", s);
     return WINO_OK;
 }
 

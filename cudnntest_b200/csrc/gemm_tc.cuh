@@ -11,8 +11,4 @@ namespace wino {
 int launch_gemm_tc(int operand, const void* v, const void* u, float* m, int batches, long long t_rows, long long tp,
                    int k, int cp, int kq, cudaStream_t st);
 
-// Device-side status word of the tensor-core kernels: 0 = fine, otherwise the code of the first bounded
-// wait that gave up.  Reading it synchronises the device and clears it.
-int read_and_clear_tc_status(int* status);
-
 }  // namespace wino

@@ -1,0 +1,95 @@
+// Thin inline-PTX wrappers shared by the TMA / mbarrier based kernels (sm_100a).
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace wino {
+
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // every device-side wait gives up after 2 s
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long global_timer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+
+// Bounded wait on an mbarrier phase.  Returns false if the CTA is aborting (abort_flag, in shared memory,
+// was raised by another thread) or if this wait ran out of time, in which case it raises the flag and
+// records `code` in the global status word (first failure wins).
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                  int code) {
+    unsigned long long t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 0xff) == 0xff) {
+            if (*abort_flag) return false;
+            const unsigned long long now = global_timer();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+// After an abort: give TMA copies that were already issued time to land before the CTA's shared memory is released.
+__device__ __forceinline__ void drain_after_abort() {
+    const unsigned long long t0 = global_timer();
+    while (global_timer() - t0 < 1000000ull) __nanosleep(1000);
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+// ---- host side (tma_host.cu) ---------------------------------------------------------------------------
+// Encodes a tiled tensor map.  dims / box are innermost first; strides_bytes has rank-1 entries (dimension 0 is
+// dense).  swizzle_128: 128-byte swizzle (inner box extent must be 128 bytes), else none.
+int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base, const unsigned long long* dims,
+                      const unsigned long long* strides_bytes, const unsigned* box, bool swizzle_128);
+int sm_count();
+// Device address of the status word the bounded waits report to (one per device, resolved once).
+int status_word(int** ptr);
+int read_and_clear_status(int* status);
+
+}  // namespace wino

@@ -1,0 +1,118 @@
+// tcgen05 / tensor-memory / TMA-store wrappers shared by the tensor-core tile GEMM kernels (sm_100a).
+#pragma once
+
+#include "ptx.cuh"
+
+namespace wino {
+
+constexpr int TC_BM = 128;                  // accumulator rows (tiles) per work unit = tensor-memory lanes
+constexpr int TC_ROW_BYTES = 128;           // bytes of contraction dimension per ring slot row (one swizzle span)
+constexpr int TC_A_BYTES = TC_BM * TC_ROW_BYTES;
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// mbarrier arrive once every tcgen05.mma issued so far by this thread has completed
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 bytes apart, 8-row groups
+// 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_k128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);   // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                    // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                    // descriptor version for tcgen05
+    d |= (uint64_t)2 << 61;                    // 128-byte swizzle
+    return d;
+}
+
+template <bool TF32>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    if (TF32) {
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "setp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+            "}\n" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "setp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+            "}\n" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
+// 32 lanes x 32 consecutive 32-bit columns of tensor memory -> 32 registers per thread
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// TMA store of one shared-memory box to a 3-D tensor (bulk async-group completion)
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src),
+                 "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// wait until at most N of this thread's bulk groups still have shared-memory reads outstanding
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// ---- host side ------------------------------------------------------------------------------------------
+// 3-D map over [batches][rows][cols] (cols contiguous); box = 128 bytes x box_rows x 1, 128-byte swizzle
+inline int make_map_k128(CUtensorMap* map, CUtensorMapDataType dt, int es, const void* ptr, int cols, long long rows,
+                         long long row_pitch, int batches, int box_rows) {
+    const unsigned long long dims[3] = {(unsigned long long)cols, (unsigned long long)rows, (unsigned long long)batches};
+    const unsigned long long strides[2] = {(unsigned long long)cols * es, (unsigned long long)row_pitch * cols * es};
+    const unsigned box[3] = {(unsigned)(TC_ROW_BYTES / es), (unsigned)box_rows, 1u};
+    return encode_tensor_map(map, dt, 3, ptr, dims, strides, box, true);
+}
+
+// tcgen05 instruction descriptor: FP32 accumulate, K-major A and B, M = 128, N = bn
+inline uint32_t make_idesc(int operand, int bn) {
+    const uint32_t fmt = operand == OP_TF32 ? 2u : operand == OP_BF16 ? 1u : 0u;  // kind::f16: 0 = F16, 1 = BF16
+    uint32_t d = 0;
+    d |= 1u << 4;                      // accumulator format: F32
+    d |= fmt << 7;                     // A format
+    d |= fmt << 10;                    // B format
+    /* bits 13, 14: no negation; bits 15, 16: A and B are K-major */
+    d |= (uint32_t)(bn >> 3) << 17;    // N / 8
+    d |= (uint32_t)(TC_BM >> 4) << 24; // M / 16
+    return d;
+}
+
+inline CUtensorMapDataType operand_map_type(int operand) {
+    return operand == OP_TF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+           : operand == OP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+}
+
+}  // namespace wino
