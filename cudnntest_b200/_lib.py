@@ -89,9 +89,12 @@ def lib():
     L.wino_stage_input_transform.argtypes = [P, V, I, I, V, V]
     L.wino_stage_gemm.argtypes = [P, V, V, V, I, V]
     L.wino_stage_output_transform.argtypes = [P, V, V, V, I, I, V]
+    L.wino_stage_gemm_rowfused.argtypes = [P, V, V, V, I, V]
+    L.wino_stage_output_transform_rowfused.argtypes = [P, V, V, V, I, I, V]
     for name in ("wino_filter_transform", "wino_conv_forward", "wino_wraped_conv", "wino_layout_convert",
                  "wino_maxpool2x2", "wino_stage_cp", "wino_stage_kq", "wino_stage_input_transform",
-                 "wino_stage_gemm", "wino_stage_output_transform"):
+                 "wino_stage_gemm", "wino_stage_output_transform", "wino_stage_gemm_rowfused",
+                 "wino_stage_output_transform_rowfused"):
         getattr(L, name).restype = I
     _lib = L
     return L

@@ -109,6 +109,17 @@ int make_geometry(const wino_conv_desc* d, Geometry* g) {
     g->tiles_img = g->bny * g->bnx;
     g->cp = round_up(d->c, 8);
     g->kq = round_up(d->k, 8);
+    // What wino_conv_forward's tile GEMM writes.  The exact-FP32 path keeps the raw products M.  The tensor-core
+    // paths write the row-transformed products Z (float for TF32, half for BF16 storage) when the layer is bound
+    // by product traffic (C <= 128); for wider layers the tile GEMM is bound by filling shared memory with
+    // operands and the 128-filter tiles of the plain kernel win.  WINO_ROWFUSE=0/1 forces either choice.
+    {
+        static const int force = [] { const char* e = getenv("WINO_ROWFUSE"); return e ? atoi(e) : -1; }();
+        const bool fuse = g->operand != OP_F32 && (force >= 0 ? force != 0 : d->c <= 128);
+        g->prod_kind = !fuse ? 0 : g->operand == OP_TF32 ? 1 : 2;
+    }
+    g->prod_planes = g->prod_kind == 0 ? g->a * g->a : g->a * g->m;
+    g->esize_prod = g->prod_kind == 2 ? 2 : 4;
     return WINO_OK;
 }
 
@@ -122,7 +133,7 @@ static long long slab_budget_bytes() {
 }
 
 long long per_image_bytes(const Geometry& g) {
-    return (long long)g.a * g.a * g.tiles_img * ((long long)g.cp * g.esize_op + (long long)g.kq * 4);
+    return (long long)g.tiles_img * ((long long)g.a * g.a * g.cp * g.esize_op + (long long)g.prod_planes * g.kq * g.esize_prod);
 }
 
 // images per slab
@@ -144,11 +155,30 @@ size_t m_bytes(const Geometry& g, long long tp) {
     return (size_t)round_up_ll((long long)g.a * g.a * tp * g.kq * 4, 1024);
 }
 
+size_t prod_bytes(const Geometry& g, long long tp) {
+    return (size_t)round_up_ll((long long)g.prod_planes * tp * g.kq * g.esize_prod, 1024);
+}
+
 int run_gemm(const Geometry& g, const void* v, const void* u, float* m, int k, long long t_rows, long long tp,
                     cudaStream_t st) {
     if (g.operand == OP_F32)
         return launch_gemm_ffma((const float*)v, (const float*)u, m, g.a * g.a, t_rows, tp, k, g.cp, g.kq, st);
     return launch_gemm_tc(g.operand, v, u, m, g.a * g.a, t_rows, tp, k, g.cp, g.kq, st);
+}
+
+int run_conv_gemm(const Geometry& g, const void* v, const void* u, void* prod, int k, long long t_rows, long long tp,
+                  cudaStream_t st) {
+    if (g.prod_kind == 0) return run_gemm(g, v, u, (float*)prod, k, t_rows, tp, st);
+    return launch_gemm_tc_z(g.operand, g.a, v, u, prod, t_rows, tp, k, g.cp, g.kq, st);
+}
+
+// stage-level entry points of the row-fused pair use Z whatever the layer width
+static bool force_rowfused(Geometry* g) {
+    if (g->operand == OP_F32) return false;
+    g->prod_kind = g->operand == OP_TF32 ? 1 : 2;
+    g->prod_planes = g->a * g->m;
+    g->esize_prod = g->prod_kind == 2 ? 2 : 4;
+    return true;
 }
 
 int check_device() {
@@ -218,7 +248,7 @@ size_t wino_conv_workspace_bytes(const wino_conv_desc* d) {
     Geometry g;
     if (make_geometry(d, &g) != WINO_OK) return 0;
     const long long tp = tile_rows(g, slab_images(*d, g));
-    return v_bytes(g, tp) + m_bytes(g, tp) + 1024;
+    return v_bytes(g, tp) + prod_bytes(g, tp) + 1024;
 }
 
 long long wino_stage_tile_rows(const wino_conv_desc* d, int ns) {
@@ -277,7 +307,31 @@ int wino_stage_output_transform(const wino_conv_desc* d, const float* m, const f
     if (d->has_bias && !bias) return fail(WINO_E_BADARG, "output transform: has_bias set but bias is NULL");
     if (n0 < 0 || ns < 0 || n0 + ns > d->n) return fail(WINO_E_BADARG, "output transform: slab [%d, %d) outside batch %d", n0, n0 + ns, d->n);
     if ((rc = check_device())) return rc;
-    return launch_output_transform(*d, g, m, bias, y, n0, ns, tile_rows(g, ns), (cudaStream_t)stream);
+    return launch_output_transform(*d, g, m, 0, bias, y, n0, ns, tile_rows(g, ns), (cudaStream_t)stream);
+}
+
+int wino_stage_gemm_rowfused(const wino_conv_desc* d, const void* v, const void* u, void* z, int ns, wino_stream_t stream) {
+    Geometry g;
+    int rc = make_geometry(d, &g);
+    if (rc) return rc;
+    if (!force_rowfused(&g)) return fail(WINO_E_UNSUPPORTED, "row-fused tile gemm exists for the tensor-core variants (TF32, BF16) only");
+    if (!v || !u || !z) return fail(WINO_E_BADARG, "row-fused tile gemm: NULL pointer");
+    if (ns < 0) return fail(WINO_E_BADARG, "row-fused tile gemm: negative slab");
+    if ((rc = check_device())) return rc;
+    return run_conv_gemm(g, v, u, z, d->k, (long long)ns * g.tiles_img, tile_rows(g, ns), (cudaStream_t)stream);
+}
+
+int wino_stage_output_transform_rowfused(const wino_conv_desc* d, const void* z, const float* bias, void* y, int n0, int ns,
+                                         wino_stream_t stream) {
+    Geometry g;
+    int rc = make_geometry(d, &g);
+    if (rc) return rc;
+    if (!force_rowfused(&g)) return fail(WINO_E_UNSUPPORTED, "row-fused output transform exists for the tensor-core variants (TF32, BF16) only");
+    if (!z || !y) return fail(WINO_E_BADARG, "row-fused output transform: NULL pointer");
+    if (d->has_bias && !bias) return fail(WINO_E_BADARG, "row-fused output transform: has_bias set but bias is NULL");
+    if (n0 < 0 || ns < 0 || n0 + ns > d->n) return fail(WINO_E_BADARG, "row-fused output transform: slab [%d, %d) outside batch %d", n0, n0 + ns, d->n);
+    if ((rc = check_device())) return rc;
+    return launch_output_transform(*d, g, z, g.prod_kind, bias, y, n0, ns, tile_rows(g, ns), (cudaStream_t)stream);
 }
 
 int wino_conv_forward(const wino_conv_desc* d, const void* x, const void* u, const float* bias, void* y,
@@ -291,19 +345,19 @@ int wino_conv_forward(const wino_conv_desc* d, const void* x, const void* u, con
     if ((rc = check_device())) return rc;
     const int ns = slab_images(*d, g);
     const long long tp = tile_rows(g, ns);
-    const size_t need = v_bytes(g, tp) + m_bytes(g, tp) + 1024;
+    const size_t need = v_bytes(g, tp) + prod_bytes(g, tp) + 1024;
     if (!workspace || workspace_bytes < need)
         return fail(WINO_E_WORKSPACE, "conv forward: workspace of %zu bytes given, %zu needed", workspace_bytes, need);
     // carve the workspace on 1 KiB boundaries
     uintptr_t base = ((uintptr_t)workspace + 1023) & ~(uintptr_t)1023;
     void* v = (void*)base;
-    float* m = (float*)(base + v_bytes(g, tp));
+    void* prod = (void*)(base + v_bytes(g, tp));
     cudaStream_t st = (cudaStream_t)stream;
     for (int n0 = 0; n0 < d->n; n0 += ns) {
         const int cur = d->n - n0 < ns ? d->n - n0 : ns;
         if ((rc = launch_input_transform(*d, g, x, n0, cur, v, tp, st))) return rc;
-        if ((rc = run_gemm(g, v, u, m, d->k, (long long)cur * g.tiles_img, tp, st))) return rc;
-        if ((rc = launch_output_transform(*d, g, m, bias, y, n0, cur, tp, st))) return rc;
+        if ((rc = run_conv_gemm(g, v, u, prod, d->k, (long long)cur * g.tiles_img, tp, st))) return rc;
+        if ((rc = launch_output_transform(*d, g, prod, g.prod_kind, bias, y, n0, cur, tp, st))) return rc;
     }
     return WINO_OK;
 }
@@ -333,7 +387,7 @@ int wino_wraped_conv(int layout_src, int layout_dst, int bat4Conv, int inside, i
             const int cur = d.n - n0 < ns ? d.n - n0 : ns;
             if ((rc = launch_input_transform(d, g, m1, n0, cur, inputTran_gpu, tp, 0))) return rc;
             if ((rc = run_gemm(g, inputTran_gpu, filterTran_gpu, gemmOutput_gpu, d.k, (long long)cur * g.tiles_img, tp, 0))) return rc;
-            if ((rc = launch_output_transform(d, g, gemmOutput_gpu, nullptr, *output, n0, cur, tp, 0))) return rc;
+            if ((rc = launch_output_transform(d, g, gemmOutput_gpu, 0, nullptr, *output, n0, cur, tp, 0))) return rc;
         }
     }
     WINO_CUDA_CHECK(cudaDeviceSynchronize());  // the reference wrappers return synchronised (wrapedConv_NCHW.cuh:482)

@@ -85,6 +85,9 @@ struct Geometry {
     int operand;      // OperandKind of V and U
     int esize_io;     // bytes per activation element
     int esize_op;     // bytes per V/U element
+    int prod_kind;    // what the tile GEMM of wino_conv_forward writes: 0 = M (float), 1 = Z (float), 2 = Z (half)
+    int prod_planes;  // a*a for M, a*m for Z
+    int esize_prod;   // bytes per product element
 };
 
 inline int round_up(int x, int q) { return (x + q - 1) / q * q; }
@@ -107,7 +110,10 @@ int make_geometry(const wino_conv_desc* d, Geometry* g);   // validates the desc
 long long per_image_bytes(const Geometry& g);              // V + M bytes one image contributes to a slab
 long long tile_rows(const Geometry& g, int ns);            // rows per V/M plane for a slab of ns images
 size_t v_bytes(const Geometry& g, long long tp);
-size_t m_bytes(const Geometry& g, long long tp);
+size_t m_bytes(const Geometry& g, long long tp);          // raw product buffer M (stage-level entry points)
+size_t prod_bytes(const Geometry& g, long long tp);       // product buffer of wino_conv_forward (M or Z)
+int run_conv_gemm(const Geometry& g, const void* v, const void* u, void* prod, int k, long long t_rows, long long tp,
+                  cudaStream_t st);
 int run_gemm(const Geometry& g, const void* v, const void* u, float* m, int k, long long t_rows, long long tp,
              cudaStream_t st);
 int check_device();
@@ -127,7 +133,8 @@ struct ProfScope {
 int launch_filter_transform(const wino_conv_desc& d, const Geometry& g, const void* w, void* u, cudaStream_t st);
 int launch_input_transform(const wino_conv_desc& d, const Geometry& g, const void* x, int n0, int ns, void* v,
                            long long tp, cudaStream_t st);
-int launch_output_transform(const wino_conv_desc& d, const Geometry& g, const float* m, const float* bias,
+// prod_kind: 0 = raw products M[a*a] (float), 1 = row-transformed Z[a*m] (float), 2 = Z (half)
+int launch_output_transform(const wino_conv_desc& d, const Geometry& g, const void* m, int prod_kind, const float* bias,
                             void* y, int n0, int ns, long long tp, cudaStream_t st);
 int launch_gemm_ffma(const float* v, const float* u, float* m, int batches, long long t_rows, long long tp, int k,
                      int cp, int kq, cudaStream_t st);

@@ -68,7 +68,7 @@ int wino_conv_forward_static(const wino_conv_desc* d, const void* x, const void*
     if ((rc = check_device())) return rc;
 
     // largest slab whose V + M (with the same 1 KiB carving as wino_conv_forward) fits the array
-    const size_t one = v_bytes(g, tile_rows(g, 1)) + m_bytes(g, tile_rows(g, 1)) + 1024;
+    const size_t one = v_bytes(g, tile_rows(g, 1)) + prod_bytes(g, tile_rows(g, 1)) + 1024;
     if (one > kStaticScratchBytes)
         return fail(WINO_E_WORKSPACE,
                     "conv forward (static scratch): one image needs %zu bytes of scratch, the built-in array holds %zu; "
@@ -77,8 +77,8 @@ int wino_conv_forward_static(const wino_conv_desc* d, const void* x, const void*
     if (ns > d->n) ns = d->n;
     if (ns > 65535) ns = 65535;
     if (ns < 1) ns = 1;
-    while (ns > 1 && v_bytes(g, tile_rows(g, ns)) + m_bytes(g, tile_rows(g, ns)) + 1024 > kStaticScratchBytes) --ns;
-    if (v_bytes(g, tile_rows(g, ns)) + m_bytes(g, tile_rows(g, ns)) + 1024 > kStaticScratchBytes)
+    while (ns > 1 && v_bytes(g, tile_rows(g, ns)) + prod_bytes(g, tile_rows(g, ns)) + 1024 > kStaticScratchBytes) --ns;
+    if (v_bytes(g, tile_rows(g, ns)) + prod_bytes(g, tile_rows(g, ns)) + 1024 > kStaticScratchBytes)
         return fail(WINO_E_WORKSPACE, "conv forward (static scratch): a slab of %d image(s) exceeds the built-in %zu bytes", ns,
                     kStaticScratchBytes);
 
@@ -87,13 +87,13 @@ int wino_conv_forward_static(const wino_conv_desc* d, const void* x, const void*
     const long long tp = tile_rows(g, ns);
     const uintptr_t base = ((uintptr_t)scratch + 1023) & ~(uintptr_t)1023;
     void* v = (void*)base;
-    float* m = (float*)(base + v_bytes(g, tp));
+    void* prod = (void*)(base + v_bytes(g, tp));
     cudaStream_t st = (cudaStream_t)stream;
     for (int n0 = 0; n0 < d->n; n0 += ns) {
         const int cur = d->n - n0 < ns ? d->n - n0 : ns;
         if ((rc = launch_input_transform(*d, g, x, n0, cur, v, tp, st))) return rc;
-        if ((rc = run_gemm(g, v, u, m, d->k, (long long)cur * g.tiles_img, tp, st))) return rc;
-        if ((rc = launch_output_transform(*d, g, m, bias, y, n0, cur, tp, st))) return rc;
+        if ((rc = run_conv_gemm(g, v, u, prod, d->k, (long long)cur * g.tiles_img, tp, st))) return rc;
+        if ((rc = launch_output_transform(*d, g, prod, g.prod_kind, bias, y, n0, cur, tp, st))) return rc;
     }
     return WINO_OK;
 }

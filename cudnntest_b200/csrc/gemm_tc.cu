@@ -180,7 +180,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant__
                                                           __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
                     fence_async_shared();
                     __syncwarp();
-                    if (lane == 0) tma_store_3d(&tm_m, stage_s + buf * TC_STORE_TILE, col0, (int)row0, xi);
+                    if (lane == 0) {
+                        tma_store_3d(&tm_m, stage_s + buf * TC_STORE_TILE, col0, (int)row0, xi);
+                        tma_store_commit();
+                    }
                     ++issued;
                 }
             }

@@ -11,4 +11,9 @@ namespace wino {
 int launch_gemm_tc(int operand, const void* v, const void* u, float* m, int batches, long long t_rows, long long tp,
                    int k, int cp, int kq, cudaStream_t st);
 
+// Row-fused variant: Z[i*m + q][t][k] = sum_j M[i*a + j][t][k] * A[j][q]; Z is float for OP_TF32, half otherwise.
+// V, U as above with a*a batches; Z: [a*m][tp][kq].
+int launch_gemm_tc_z(int operand, int a, const void* v, const void* u, void* z, long long t_rows, long long tp, int k, int cp,
+                     int kq, cudaStream_t st);
+
 }  // namespace wino

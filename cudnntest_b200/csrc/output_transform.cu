@@ -19,7 +19,7 @@
 namespace wino {
 
 struct OTArgs {
-    const float* m;
+    const void* m;       // products M[a*a][tp][kq] (float) or row-transformed Z[a*m][tp][kq] (float / half)
     const float* bias;
     void* y;
     int K;
@@ -37,20 +37,40 @@ constexpr int OT_KB = 32;
 constexpr int OT_TX = 8;
 constexpr int OT_NB = 8;
 
-// Loads the a*a products of (tile t, filter k), applies A^T . A, bias, ReLU and (POOL) the 2x2 max.
+// Loads the products of (tile t, filter k) and finishes the output transform, then bias, ReLU and (POOL) the 2x2
+// max.  ZF = false: the buffer holds the a*a raw products M and both 1-D transforms run here.  ZF = true: the
+// buffer holds Z = M A (a*m values, written by the row-fused tile GEMM) and only A^T along i is left.
 // res[p][q] holds the MO x MO stored outputs of the tile, MO = M or M/2.
-template <int A, bool POOL>
+template <int A, bool POOL, bool ZF, typename TP>
 __device__ __forceinline__ void tile_outputs(const OTArgs& a, long long t, int k,
                                              float (&res)[POOL ? (A - 2) / 2 : (A - 2)][POOL ? (A - 2) / 2 : (A - 2)]) {
     constexpr int M = A - 2;
-    float mm[A][A], y[M][M];
+    float y[M][M];
     const long long plane = a.tp * a.kq;
-    const float* src = a.m + t * a.kq + k;
+    const TP* src = reinterpret_cast<const TP*>(a.m) + t * a.kq + k;
+    if constexpr (ZF) {
+        float z[A][M];
 #pragma unroll
-    for (int i = 0; i < A; ++i)
+        for (int i = 0; i < A; ++i)
 #pragma unroll
-        for (int j = 0; j < A; ++j) mm[i][j] = __ldg(src + (long long)(i * A + j) * plane);
-    output_tile_transform<A>(mm, y);
+            for (int q = 0; q < M; ++q) z[i][q] = to_float<TP>(src[(long long)(i * M + q) * plane]);
+#pragma unroll
+        for (int q = 0; q < M; ++q) {
+            float col[A], out[M];
+#pragma unroll
+            for (int i = 0; i < A; ++i) col[i] = z[i][q];
+            at_1d<A>(col, out);
+#pragma unroll
+            for (int p = 0; p < M; ++p) y[p][q] = out[p];
+        }
+    } else {
+        float mm[A][A];
+#pragma unroll
+        for (int i = 0; i < A; ++i)
+#pragma unroll
+            for (int j = 0; j < A; ++j) mm[i][j] = to_float<TP>(src[(long long)(i * A + j) * plane]);
+        output_tile_transform<A>(mm, y);
+    }
     const float b = a.bias ? __ldg(a.bias + k) : 0.f;
 #pragma unroll
     for (int p = 0; p < M; ++p)
@@ -75,7 +95,7 @@ __device__ __forceinline__ void tile_outputs(const OTArgs& a, long long t, int k
 }
 
 // NHWC destination: direct store, lanes along k
-template <int A, bool POOL, typename TOut>
+template <int A, bool POOL, bool ZF, typename TP, typename TOut>
 __global__ void __launch_bounds__(256) output_transform_direct(OTArgs a, long long T) {
     constexpr int MO = POOL ? (A - 2) / 2 : (A - 2);
     const int kchunks = (a.K + OT_KB - 1) / OT_KB;
@@ -84,7 +104,7 @@ __global__ void __launch_bounds__(256) output_transform_direct(OTArgs a, long lo
     const long long t = item / (kchunks * OT_KB);
     if (t >= T || k >= a.K) return;
     float res[MO][MO];
-    tile_outputs<A, POOL>(a, t, k, res);
+    tile_outputs<A, POOL, ZF, TP>(a, t, k, res);
     const int tiles_img = a.bny * a.bnx;
     const int n = a.n0 + (int)(t / tiles_img);
     const int rem = (int)(t % tiles_img);
@@ -103,7 +123,7 @@ __global__ void __launch_bounds__(256) output_transform_direct(OTArgs a, long lo
 }
 
 // NCHW destination: stage TX tiles x 32 filters, store rows contiguous along w
-template <int A, bool POOL, typename TOut>
+template <int A, bool POOL, bool ZF, typename TP, typename TOut>
 __global__ void __launch_bounds__(256) output_transform_strip(OTArgs a) {
     constexpr int MO = POOL ? (A - 2) / 2 : (A - 2);
     constexpr int COLS = MO * OT_TX;
@@ -122,7 +142,7 @@ __global__ void __launch_bounds__(256) output_transform_strip(OTArgs a) {
         if (bx < a.bnx && k < a.K) {
             float res[MO][MO];
             const long long t = ((long long)blockIdx.z * a.bny + by) * a.bnx + bx;
-            tile_outputs<A, POOL>(a, t, k, res);
+            tile_outputs<A, POOL, ZF, TP>(a, t, k, res);
 #pragma unroll
             for (int p = 0; p < MO; ++p)
 #pragma unroll
@@ -143,7 +163,7 @@ __global__ void __launch_bounds__(256) output_transform_strip(OTArgs a) {
 }
 
 // CHWN destination: stage 8 images x 32 filters of one tile position, store contiguous along n
-template <int A, bool POOL, typename TOut>
+template <int A, bool POOL, bool ZF, typename TP, typename TOut>
 __global__ void __launch_bounds__(256) output_transform_batch(OTArgs a) {
     constexpr int MO = POOL ? (A - 2) / 2 : (A - 2);
     constexpr int PITCH = OT_KB + 4;
@@ -160,7 +180,7 @@ __global__ void __launch_bounds__(256) output_transform_batch(OTArgs a) {
         if (nb0 + n_l < a.ns && k < a.K) {
             float res[MO][MO];
             const long long t = ((long long)(nb0 + n_l) * a.bny + by) * a.bnx + bx;
-            tile_outputs<A, POOL>(a, t, k, res);
+            tile_outputs<A, POOL, ZF, TP>(a, t, k, res);
 #pragma unroll
             for (int p = 0; p < MO; ++p)
 #pragma unroll
@@ -181,7 +201,7 @@ __global__ void __launch_bounds__(256) output_transform_batch(OTArgs a) {
     }
 }
 
-template <int A, bool POOL, typename TOut>
+template <int A, bool POOL, bool ZF, typename TP, typename TOut>
 static int run(const wino_conv_desc& d, const Geometry& g, const OTArgs& a, cudaStream_t st) {
     static_assert(OT_TX * OT_KB == 256 && OT_NB * OT_KB == 256, "one work item per thread");
     const int kchunks = (d.k + OT_KB - 1) / OT_KB;
@@ -190,27 +210,28 @@ static int run(const wino_conv_desc& d, const Geometry& g, const OTArgs& a, cuda
     if (d.layout_out == WINO_NHWC) {
         const long long T = (long long)a.ns * g.tiles_img;
         const long long items = T * kchunks * OT_KB;
-        output_transform_direct<A, POOL, TOut><<<(unsigned)((items + 255) / 256), 256, 0, st>>>(a, T);
+        output_transform_direct<A, POOL, ZF, TP, TOut><<<(unsigned)((items + 255) / 256), 256, 0, st>>>(a, T);
     } else if (d.layout_out == WINO_NCHW) {
         dim3 grid((unsigned)(((g.bnx + OT_TX - 1) / OT_TX) * kchunks), (unsigned)g.bny, (unsigned)a.ns);
-        output_transform_strip<A, POOL, TOut><<<grid, 256, 0, st>>>(a);
+        output_transform_strip<A, POOL, ZF, TP, TOut><<<grid, 256, 0, st>>>(a);
     } else {
         dim3 grid((unsigned)(((a.ns + OT_NB - 1) / OT_NB) * kchunks), (unsigned)g.bnx, (unsigned)g.bny);
-        output_transform_batch<A, POOL, TOut><<<grid, 256, 0, st>>>(a);
+        output_transform_batch<A, POOL, ZF, TP, TOut><<<grid, 256, 0, st>>>(a);
     }
     WINO_CUDA_CHECK(cudaGetLastError());
     return WINO_OK;
 }
 
-template <int A>
+template <int A, bool ZF, typename TP>
 static int dispatch(const wino_conv_desc& d, const Geometry& g, const OTArgs& a, cudaStream_t st) {
     const bool bf16 = d.dtype == WINO_BF16;
     if (d.pool2x2)
-        return bf16 ? run<A, true, __nv_bfloat16>(d, g, a, st) : run<A, true, float>(d, g, a, st);
-    return bf16 ? run<A, false, __nv_bfloat16>(d, g, a, st) : run<A, false, float>(d, g, a, st);
+        return bf16 ? run<A, true, ZF, TP, __nv_bfloat16>(d, g, a, st) : run<A, true, ZF, TP, float>(d, g, a, st);
+    return bf16 ? run<A, false, ZF, TP, __nv_bfloat16>(d, g, a, st) : run<A, false, ZF, TP, float>(d, g, a, st);
 }
 
-int launch_output_transform(const wino_conv_desc& d, const Geometry& g, const float* m, const float* bias,
+// prod_kind: 0 = raw products M (float), 1 = row-transformed Z (float), 2 = row-transformed Z (half)
+int launch_output_transform(const wino_conv_desc& d, const Geometry& g, const void* m, int prod_kind, const float* bias,
                             void* y, int n0, int ns, long long tp, cudaStream_t st) {
     if (ns <= 0) return WINO_OK;
     if (ns > 65535 || g.bny > 65535 || g.bnx > 65535)
@@ -222,7 +243,10 @@ int launch_output_transform(const wino_conv_desc& d, const Geometry& g, const fl
     a.n0 = n0; a.ns = ns; a.bny = g.bny; a.bnx = g.bnx; a.kq = g.kq; a.tp = tp;
     a.relu = d.relu; a.pool = d.pool2x2;
     a.sy = act_strides(d.layout_out, d.n, d.k, g.ph, g.pw);
-    return g.a == 6 ? dispatch<6>(d, g, a, st) : dispatch<4>(d, g, a, st);
+    if (prod_kind == 0) return g.a == 6 ? dispatch<6, false, float>(d, g, a, st) : dispatch<4, false, float>(d, g, a, st);
+    if (prod_kind == 1) return g.a == 6 ? dispatch<6, true, float>(d, g, a, st) : dispatch<4, true, float>(d, g, a, st);
+    if (prod_kind == 2) return g.a == 6 ? dispatch<6, true, __half>(d, g, a, st) : dispatch<4, true, __half>(d, g, a, st);
+    return fail(WINO_E_BADARG, "output transform: bad product kind %d", prod_kind);
 }
 
 }  // namespace wino

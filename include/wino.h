@@ -163,6 +163,17 @@ int wino_stage_gemm(const wino_conv_desc* d, const void* v, const void* u, float
 int wino_stage_output_transform(const wino_conv_desc* d, const float* m, const float* bias, void* y, int n0,
                                 int ns, wino_stream_t stream);
 
+/* Row-fused pair used by wino_conv_forward for the tensor-core variants (WINO_TF32, WINO_BF16): the tile
+ * GEMM applies the first 1-D output transform in its epilogue and writes
+ *   Z[i*m + q][Tp][Kq] = sum_j M[i*a + j] * A[j][q]      (float for WINO_TF32, IEEE half for WINO_BF16)
+ * instead of the a*a raw products; the output transform then only applies A^T along i.  Together they
+ * replace GEMM_batch_256_128x128_* + wino_invers_* (comparison/GEMM.cuh:124-255,
+ * comparison/wrapedConv_NCHW.cuh:1034-1114) with a third (TF32: two thirds) of the product traffic. */
+int wino_stage_gemm_rowfused(const wino_conv_desc* d, const void* v, const void* u, void* z, int ns,
+                             wino_stream_t stream);
+int wino_stage_output_transform_rowfused(const wino_conv_desc* d, const void* z, const float* bias, void* y,
+                                         int n0, int ns, wino_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -46,14 +46,17 @@ def test_buffer_sizes(L, shape, dtype, m):
     assert L.wino_filter_bytes(dp) == a * a * k * cp * es
     tiles = math.ceil(h / m) * math.ceil(w / m)
     assert L.wino_stage_tile_rows(dp, 3) == math.ceil(3 * tiles / 128) * 128
-    # the default slab keeps V + M of one pass within the L2 budget unless a single image exceeds it
+    # scratch = V + product buffer of one slab; the product buffer is M (a*a float planes) for FP32 and for wide
+    # layers, Z (a*m planes, half for BF16) where the row-fused tile GEMM is used
     ws = L.wino_conv_workspace_bytes(dp)
-    per_image = a * a * tiles * (cp * es + kq * 4)
-    assert ws >= per_image
-    assert ws <= max(2048 << 20, per_image) + a * a * 128 * (cp * es + kq * 4) + 4096
-    # an explicit slab of the whole batch needs the whole-batch buffers
+    v_img = a * a * tiles * cp * es
+    assert ws >= v_img + a * m * tiles * kq * 2
     d.slab_images = n
-    assert L.wino_conv_workspace_bytes(dp) >= n * per_image
+    ws_all = L.wino_conv_workspace_bytes(dp)
+    assert ws_all >= n * (v_img + a * m * tiles * kq * 2)
+    if dtype == "fp32":
+        assert ws_all >= n * (v_img + a * a * tiles * kq * 4)
+    assert ws_all <= n * (v_img + a * a * tiles * kq * 4) + a * a * 128 * (cp * es + kq * 4) + 4096
 
 
 def test_legacy_workspaces_cover_the_slabs(L):

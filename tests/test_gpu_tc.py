@@ -55,6 +55,46 @@ def test_tile_gemm_alone(cb, dtype, operand, kind, shape):
     assert np.all(got[:, :t, k:] == 0)
 
 
+@pytest.mark.parametrize("dtype,kind,m", [("tf32", "tf32", 4), ("tf32", "tf32", 2), ("bf16", "f16", 4), ("bf16", "f16", 2)])
+@pytest.mark.parametrize("shape", [(200, 64, 64), (130, 24, 40), (700, 256, 200)])
+def test_rowfused_gemm_and_output_transform(cb, dtype, kind, m, shape):
+    """Z = M A from the fused epilogue vs the same product computed in float64, then the remaining half of the
+    output transform against the stage oracle."""
+    import torch
+    t, c, k = shape
+    a = m + 2
+    d = cb.make_desc(t, c, m, m, k, layout="NHWC", dtype=dtype, wino=m, relu=True, bias=True)   # one tile per image
+    L = cb.lib()
+    dp = ctypes.byref(d)
+    cp, kq, tp = L.wino_stage_cp(dp), L.wino_stage_kq(dp), L.wino_stage_tile_rows(dp, t)
+    rng = np.random.default_rng(t + c + k + m)
+    v = np.zeros((a * a, tp, cp), dtype=np.float32)
+    u = np.zeros((a * a, k, cp), dtype=np.float32)
+    v[:, :t, :c] = oracle.round_to(rng.uniform(-4, 4, (a * a, t, c)).astype(np.float32), kind)
+    u[:, :, :c] = oracle.round_to((rng.standard_normal((a * a, k, c)) * 0.05).astype(np.float32), kind)
+    tdt = {"tf32": torch.float32, "f16": torch.float16}[kind]
+    zdt = torch.float32 if dtype == "tf32" else torch.float16
+    vd, ud = to_dev(v, tdt), to_dev(u, tdt)
+    z = torch.full((a * m, tp, kq), float("nan"), dtype=zdt, device="cuda")
+    P = lambda q: ctypes.c_void_p(q.data_ptr())
+    cb._lib.check(L.wino_stage_gemm_rowfused(dp, P(vd), P(ud), P(z), t, None))
+    cb.device_status()
+    mm = oracle.tile_gemm(v[:, :t, :c], u[:, :, :c]).reshape(a, a, t, k)
+    _, _, at = oracle.matrices(m)
+    zref = np.einsum("ijtk,qj->iqtk", mm, at).reshape(a * m, t, k)
+    got = z.float().cpu().numpy()
+    assert np.isfinite(got[:, :t, :k]).all()
+    assert maxrel(got[:, :t, :k], zref) <= (2e-6 if dtype == "tf32" else 1e-3)    # half: 2^-11 rounding of Z
+    # second half of the output transform
+    b = (rng.standard_normal(k) * 0.1).astype(np.float32)
+    tio = torch.bfloat16 if dtype == "bf16" else torch.float32
+    y = torch.full((t, m, m, k), float("nan"), dtype=tio, device="cuda")
+    cb._lib.check(L.wino_stage_output_transform_rowfused(dp, P(z), P(to_dev(b)), P(y), 0, t, None))
+    cb.device_status()
+    yref = oracle.output_transform(mm.reshape(a * a, t, k), t, m, m, 1, m, bias=b, relu=True)   # (t, k, m, m)
+    assert rel_l2(oracle.from_layout(y.float().cpu().numpy(), "NHWC"), yref) <= (1e-5 if dtype == "tf32" else 4e-3)
+
+
 @pytest.mark.parametrize("layout", LAYOUTS)
 @pytest.mark.parametrize("dtype,wino,operand", [("tf32", 4, 0), ("tf32", 2, 0), ("bf16", 4, 0), ("bf16", 2, 0), ("bf16", 4, 1)])
 def test_conv_reduced_precision(cb, layout, dtype, wino, operand):
