@@ -241,7 +241,9 @@ int wino_device_status(void) {
 size_t wino_filter_bytes(const wino_conv_desc* d) {
     Geometry g;
     if (make_geometry(d, &g) != WINO_OK) return 0;
-    return (size_t)g.a * g.a * d->k * g.cp * g.esize_op;
+    const size_t wino = (size_t)g.a * g.a * d->k * g.cp * g.esize_op;
+    // thin-input layers keep packed raw filters instead (always smaller); report the larger so either path fits
+    return direct_small_c_applies(*d) && direct_small_c_filter_bytes(*d) > wino ? direct_small_c_filter_bytes(*d) : wino;
 }
 
 size_t wino_conv_workspace_bytes(const wino_conv_desc* d) {
@@ -275,6 +277,7 @@ int wino_filter_transform(const wino_conv_desc* d, const void* w, void* u, wino_
     if (rc) return rc;
     if (!w || !u) return fail(WINO_E_BADARG, "filter transform: NULL pointer");
     if ((rc = check_device())) return rc;
+    if (direct_small_c_applies(*d)) return launch_direct_small_c_pack(*d, w, u, (cudaStream_t)stream);
     return launch_filter_transform(*d, g, w, u, (cudaStream_t)stream);
 }
 
@@ -343,6 +346,7 @@ int wino_conv_forward(const wino_conv_desc* d, const void* x, const void* u, con
     if (!x || !u || !y) return fail(WINO_E_BADARG, "conv forward: NULL tensor pointer");
     if (d->has_bias && !bias) return fail(WINO_E_BADARG, "conv forward: has_bias set but bias is NULL");
     if ((rc = check_device())) return rc;
+    if (direct_small_c_applies(*d)) return launch_direct_small_c(*d, g, x, u, bias, y, (cudaStream_t)stream);
     const int ns = slab_images(*d, g);
     const long long tp = tile_rows(g, ns);
     const size_t need = v_bytes(g, tp) + prod_bytes(g, tp) + 1024;

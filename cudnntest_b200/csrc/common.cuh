@@ -138,6 +138,12 @@ int launch_output_transform(const wino_conv_desc& d, const Geometry& g, const vo
                             void* y, int n0, int ns, long long tp, cudaStream_t st);
 int launch_gemm_ffma(const float* v, const float* u, float* m, int batches, long long t_rows, long long tp, int k,
                      int cp, int kq, cudaStream_t st);
+// thin-input (C <= 3) direct convolution on tensor cores (direct_small_c.cu)
+bool direct_small_c_applies(const wino_conv_desc& d);
+size_t direct_small_c_filter_bytes(const wino_conv_desc& d);
+int launch_direct_small_c_pack(const wino_conv_desc& d, const void* w, void* packed, cudaStream_t st);
+int launch_direct_small_c(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias,
+                          void* y, cudaStream_t st);
 int launch_relayout(int src, int dst, int n, int c, int h, int w, int esize, const void* in, void* out,
                     cudaStream_t st);
 int launch_maxpool(int layout, int n, int c, int h, int w, int dtype, const void* in, void* out, cudaStream_t st);

@@ -1,0 +1,282 @@
+// Direct 3x3 convolution for very thin inputs (C <= 3: the first VGG layer, 3 -> 64 at 224 x 224), sm_100a.
+//
+// The reference sends this layer through the same Winograd pipeline with the channel count padded to 8
+// (comparison/layoutCompare.cu:43-46 "layer 1: c = 3", KSize rounding wrapedConv_NCHW.cuh:362).  With three
+// channels the 36 products per tile cost far more memory traffic than the convolution itself, so this library
+// routes the tensor-core variants of such layers to an implicit-GEMM kernel instead: the contraction is the
+// 9*C <= 27 taps, padded to 32.
+//
+//   * one thread = one output pixel.  It gathers its 3x3xC patch (zero padded) straight from the input layout
+//     and writes it as one K-major row of a 128 x 32 operand tile in shared memory, in the 128-byte-swizzled
+//     layout tcgen05.mma reads;
+//   * the 64 x 32 filter tile is built once per CTA the same way;
+//   * thread 0 issues tcgen05.mma (M = 128 pixels, N = 64 filters, K = 32) into a 64-column accumulator in tensor
+//     memory and commits to an mbarrier; every thread then reads its own accumulator lane (tcgen05.ld), adds the
+//     bias, applies ReLU and stores its pixel's 64 outputs (one contiguous 128-byte line for NHWC BF16).
+// Several CTAs share an SM so one CTA's gather overlaps another's MMA and stores.  Bound: HBM, by the output
+// write (N*K*OH*OW elements); the input is read once from HBM and nine times from L1/L2.
+#include <cstdlib>
+
+#include "common.cuh"
+#include "ptx.cuh"
+#include "tcgen05.cuh"
+
+namespace wino {
+
+namespace {
+
+constexpr int DC_WAIT_CODE = 21;
+
+struct DCArgs {
+    const void* x;
+    const void* w;
+    const float* bias;
+    void* y;
+    int N, C, H, W, K, pad;
+    int oh, ow;
+    long long pixels;      // N * oh * ow
+    int relu;
+    uint32_t idesc;
+    Strides sx, sw, sy;
+    int* status;
+};
+
+template <typename TIn>
+struct OperandRow;
+// BF16 storage: operands are the stored bf16 values themselves (32 x 2 bytes = four 16-byte chunks per row)
+template <>
+struct OperandRow<__nv_bfloat16> {
+    static constexpr bool TF32 = false;
+    static __device__ __forceinline__ void store(uint8_t* row_base, int row, const float (&v)[32]) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            uint32_t wds[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 p = __floats2bfloat162_rn(v[8 * c + 2 * e], v[8 * c + 2 * e + 1]);
+                wds[e] = *reinterpret_cast<uint32_t*>(&p);
+            }
+            *reinterpret_cast<uint4*>(row_base + ((c ^ (row & 7)) << 4)) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+        }
+    }
+};
+// float storage: operands rounded to TF32 (32 x 4 bytes = eight chunks per row)
+template <>
+struct OperandRow<float> {
+    static constexpr bool TF32 = true;
+    static __device__ __forceinline__ void store(uint8_t* row_base, int row, const float (&v)[32]) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            uint32_t wds[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) wds[e] = __float_as_uint(from_float<tf32_t>(v[4 * c + e]).v);
+            *reinterpret_cast<uint4*>(row_base + ((c ^ (row & 7)) << 4)) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+        }
+    }
+};
+
+template <typename TIn, typename TOut, int CC>
+__global__ void __launch_bounds__(128) direct_small_c_kernel(const DCArgs a) {
+    using Row = OperandRow<TIn>;
+    __shared__ __align__(1024) uint8_t a_tile[128 * 128];
+    __shared__ __align__(1024) uint8_t b_tile[64 * 128];
+    __shared__ __align__(8) unsigned long long bar_storage;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid / 32;
+    const int k0 = blockIdx.y * 64;
+    const uint32_t bar = smem_u32(&bar_storage);
+
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0) tmem_alloc(smem_u32(&tmem_slot), 64);
+
+    // filter tile: row kf = packed filter row k0 + kf (32 operand values, see pack_direct_filters), zero beyond K
+    if (tid < 64) {
+        float v[32];
+        const int kf = k0 + tid;
+        const TIn* wp = reinterpret_cast<const TIn*>(a.w) + (long long)kf * 32;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = kf < a.K ? to_float<TIn>(wp[i]) : 0.f;
+        Row::store(b_tile + tid * 128, tid, v);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    const uint32_t a_s = smem_u32(a_tile), b_s = smem_u32(b_tile);
+    const TIn* __restrict__ xin = reinterpret_cast<const TIn*>(a.x);
+    TOut* __restrict__ yout = reinterpret_cast<TOut*>(a.y);
+
+    uint32_t parity = 0;
+    const long long tiles = (a.pixels + 127) / 128;
+    for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const long long p = tile * 128 + tid;
+        const bool valid = p < a.pixels;
+        int n = 0, oy = 0, ox = 0;
+        if (valid) {
+            ox = (int)(p % a.ow);
+            const long long q = p / a.ow;
+            oy = (int)(q % a.oh);
+            n = (int)(q / a.oh);
+        }
+        {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            if (valid) {
+                const TIn* xp = xin + n * a.sx.n;
+#pragma unroll
+                for (int r = 0; r < 3; ++r) {
+                    const int ih = oy + r - a.pad;
+                    if (ih < 0 || ih >= a.H) continue;
+#pragma unroll
+                    for (int s = 0; s < 3; ++s) {
+                        const int iw = ox + s - a.pad;
+                        if (iw < 0 || iw >= a.W) continue;
+#pragma unroll
+                        for (int c = 0; c < CC; ++c)
+                            if (c < a.C) v[(r * 3 + s) * CC + c] = to_float<TIn>(xp[c * a.sx.c + ih * a.sx.h + iw * a.sx.w]);
+                    }
+                }
+            }
+            Row::store(a_tile + tid * 128, tid, v);
+        }
+        fence_async_shared();        // the tile was written through the generic proxy, tcgen05.mma reads it through the async proxy
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 4 / (Row::TF32 ? 1 : 2); ++ks)
+                tc_mma<Row::TF32>(tmem_base, smem_desc_k128(a_s + ks * 32), smem_desc_k128(b_s + ks * 32), a.idesc, ks ? 1u : 0u);
+            tc_commit(bar);
+        }
+        bool ok = mbar_wait_bounded(bar, parity, &abort_flag, a.status, DC_WAIT_CODE);
+        parity ^= 1;
+        if (!__syncthreads_and(ok)) break;
+        tc_fence_after();
+        uint32_t r0[32], r1[32];
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+        tmem_ld_32x32(lane_addr, r0);
+        tmem_ld_32x32(lane_addr + 32, r1);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncthreads();             // accumulator and operand tile may be overwritten by the next tile from here on
+        if (valid) {
+            TOut* yp = yout + n * a.sy.n + oy * a.sy.h + ox * a.sy.w;
+            if (a.sy.c == 1 && k0 + 64 <= a.K && (reinterpret_cast<uintptr_t>(yp + k0) & 15) == 0) {
+                // filters contiguous (NHWC): 16-byte stores
+                constexpr int PER = 16 / (int)sizeof(TOut);
+#pragma unroll
+                for (int c = 0; c < 64 / PER; ++c) {
+                    float o[PER];
+#pragma unroll
+                    for (int e = 0; e < PER; ++e) {
+                        const int kk = c * PER + e;
+                        const float val = __uint_as_float(kk < 32 ? r0[kk] : r1[kk - 32]) + (a.bias ? __ldg(a.bias + k0 + kk) : 0.f);
+                        o[e] = a.relu ? fmaxf(val, 0.f) : val;
+                    }
+                    uint32_t wds[4];
+                    if constexpr (sizeof(TOut) == 2) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(o[2 * e], o[2 * e + 1]);
+                            wds[e] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) wds[e] = __float_as_uint(o[e]);
+                    }
+                    *reinterpret_cast<uint4*>(yp + k0 + c * PER) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+                }
+            } else {
+#pragma unroll
+                for (int kk = 0; kk < 64; ++kk) {
+                    if (k0 + kk >= a.K) break;
+                    float val = __uint_as_float(kk < 32 ? r0[kk] : r1[kk - 32]) + (a.bias ? __ldg(a.bias + k0 + kk) : 0.f);
+                    if (a.relu) val = fmaxf(val, 0.f);
+                    yp[(long long)(k0 + kk) * a.sy.c] = from_float<TOut>(val);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 64);
+    }
+}
+
+// Packed filters for the kernel above: P[k][(r*3 + s)*3 + c] = w[k][c][r][s] through the filter layout's strides,
+// 32 values per filter (zero beyond the 9*C taps), in the operand format (bf16, or float rounded to TF32).
+template <typename TIn>
+__global__ void pack_direct_filters(const TIn* __restrict__ w, TIn* __restrict__ out, int K, int C, Strides sw) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= K * 32) return;
+    const int k = idx / 32, col = idx % 32;
+    const int rs = col / 3, c = col % 3;
+    float v = 0.f;
+    if (rs < 9 && c < C) v = to_float<TIn>(w[k * sw.n + c * sw.c + (rs / 3) * sw.h + (rs % 3) * sw.w]);
+    if (sizeof(TIn) == 4) v = from_float<tf32_t>(v).v;
+    out[idx] = from_float<TIn>(v);
+}
+
+template <typename TIn, typename TOut>
+int run(const DCArgs& a, cudaStream_t st) {
+    const long long tiles = (a.pixels + 127) / 128;
+    const long long max_ctas = 6LL * sm_count();
+    dim3 grid((unsigned)(tiles < max_ctas ? tiles : max_ctas), (unsigned)((a.K + 63) / 64));
+    ProfScope prof(STAGE_GEMM, st);
+    count_launch();
+    direct_small_c_kernel<TIn, TOut, 3><<<grid, 128, 0, st>>>(a);
+    WINO_CUDA_CHECK(cudaGetLastError());
+    return WINO_OK;
+}
+
+}  // namespace
+
+bool direct_small_c_applies(const wino_conv_desc& d) {
+    static const bool off = [] { const char* e = getenv("WINO_NO_DIRECT"); return e && e[0] == '1'; }();
+    return !off && d.c <= 3 && !d.pool2x2 && (d.dtype == WINO_BF16 || d.dtype == WINO_TF32);
+}
+
+size_t direct_small_c_filter_bytes(const wino_conv_desc& d) { return (size_t)d.k * 32 * (d.dtype == WINO_BF16 ? 2 : 4); }
+
+int launch_direct_small_c_pack(const wino_conv_desc& d, const void* w, void* packed, cudaStream_t st) {
+    const int total = d.k * 32;
+    const Strides sw = filter_strides(d.layout_in, d.k, d.c);
+    ProfScope prof(STAGE_FILTER, st);
+    count_launch();
+    if (d.dtype == WINO_BF16)
+        pack_direct_filters<__nv_bfloat16><<<(total + 255) / 256, 256, 0, st>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)packed, d.k, d.c, sw);
+    else
+        pack_direct_filters<float><<<(total + 255) / 256, 256, 0, st>>>((const float*)w, (float*)packed, d.k, d.c, sw);
+    WINO_CUDA_CHECK(cudaGetLastError());
+    return WINO_OK;
+}
+
+// `w` is the packed filter buffer written by launch_direct_small_c_pack
+int launch_direct_small_c(const wino_conv_desc& d, const Geometry& g, const void* x, const void* w, const float* bias,
+                          void* y, cudaStream_t st) {
+    DCArgs a;
+    a.x = x; a.w = w; a.bias = d.has_bias ? bias : nullptr; a.y = y;
+    a.N = d.n; a.C = d.c; a.H = d.h; a.W = d.w; a.K = d.k; a.pad = d.pad;
+    a.oh = g.oh; a.ow = g.ow;
+    a.pixels = (long long)d.n * g.oh * g.ow;
+    a.relu = d.relu;
+    a.idesc = make_idesc(d.dtype == WINO_TF32 ? OP_TF32 : OP_BF16, 64);
+    a.sx = act_strides(d.layout_in, d.n, d.c, d.h, d.w);
+    a.sw = filter_strides(d.layout_in, d.k, d.c);   // unused by the kernel: the filters arrive packed
+    a.sy = act_strides(d.layout_out, d.n, d.k, g.oh, g.ow);
+    if (a.pixels == 0) return WINO_OK;
+    int rc = status_word(&a.status);
+    if (rc) return rc;
+    return d.dtype == WINO_BF16 ? run<__nv_bfloat16, __nv_bfloat16>(a, st) : run<float, float>(a, st);
+}
+
+}  // namespace wino

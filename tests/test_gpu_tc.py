@@ -123,6 +123,31 @@ def test_conv_bf16_ragged(cb, shape):
         assert rel_l2(y, ref) <= TOL_L2
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "tf32"])
+@pytest.mark.parametrize("layout", LAYOUTS)
+@pytest.mark.parametrize("shape", [(2, 3, 20, 20, 64), (1, 3, 7, 9, 40), (3, 1, 6, 6, 130), (2, 2, 5, 5, 8)])
+def test_thin_input_direct_path(cb, dtype, layout, shape):
+    """C <= 3 (the first VGG layer) runs the implicit-GEMM kernel; every layout, K not a multiple of 64."""
+    n, c, h, w, k = shape
+    x, wt, b = make_inputs(n, c, h, w, k, seed=sum(shape) + 1)
+    ref = oracle.conv_f64(x, wt, bias=b, relu=True)
+    y = run_conv(x, wt, b, layout, dtype=dtype, relu=True)
+    assert rel_l2(y, ref) <= TOL_L2
+    for lo in LAYOUTS:
+        if lo != layout:
+            y2 = run_conv(x, wt, b, layout, layout_out=lo, dtype=dtype, relu=True)
+            assert np.array_equal(y2, y)
+    y3 = run_conv(x, wt, None, layout, dtype=dtype, pad=0)
+    assert rel_l2(y3, oracle.conv_f64(x, wt, pad=0)) <= TOL_L2
+
+
+def test_first_vgg_layer_full_size(cb):
+    """3 -> 64 at 224 x 224, BF16 NHWC, 4 images: against the oracle."""
+    x, wt, b = make_inputs(4, 3, 224, 224, 64, seed=0xC0DE0041)
+    y = run_conv(x, wt, b, "NHWC", dtype="bf16", relu=True)
+    assert rel_l2(y, oracle.conv_f64(x, wt, bias=b, relu=True)) <= TOL_L2
+
+
 def test_full_size_config1_bf16(cb):
     """BASELINE config 1 at full size, BF16 NHWC: first two images vs the oracle, slab-size invariance."""
     n, c, h, k = 64, 256, 56, 256
