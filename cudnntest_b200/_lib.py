@@ -47,6 +47,9 @@ def build(force=False, verbose=False):
     if force:
         cmd.append("-B")
     subprocess.check_call(cmd, stdout=None if verbose else subprocess.DEVNULL)
+    # the harness executables (layoutCompare, layoutTest, netTest) link libwino and, for the comparator, cuDNN
+    hcmd = ["make", "-C", os.path.join(_HERE, "harness"), "-j3"] + (["-B"] if force else [])
+    subprocess.check_call(hcmd, stdout=None if verbose else subprocess.DEVNULL)
     return _SO
 
 

@@ -1,0 +1,61 @@
+"""The C++ harness executables (layoutCompare, layoutTest, netTest) run, keep the reference's output format
+("time:<ms> ms" lines that comparison/test.sh greps for) and pass their own host-side checks."""
+import json
+import os
+import re
+import subprocess
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+BIN = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "cudnntest_b200", "harness", "bin")
+
+
+def run(exe, *args):
+    p = subprocess.run([os.path.join(BIN, exe)] + list(args), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    return p.stdout
+
+
+def summary(out):
+    return json.loads([l for l in out.splitlines() if l.startswith("{")][-1])
+
+
+@pytest.mark.parametrize("opt", [0, 1, 2])
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_layout_compare_ours(opt, dtype):
+    out = run("layoutCompare", "batch=4", "opt=%d" % opt, "layer=6", "dtype=" + dtype, "iters=5")
+    assert len(re.findall(r"time:[0-9.]+ ms", out)) == 5
+    assert "moduleConv error" not in out
+    s = summary(out)
+    assert s["layout"] == ["NCHW", "NHWC", "CHWN"][opt] and s["max_err_sampled"] <= (1e-4 if dtype == "fp32" else 2e-2)
+
+
+def test_layout_compare_cudnn_best():
+    out = run("layoutCompare", "batch=4", "opt=8", "layer=6", "dtype=bf16", "iters=5")
+    s = summary(out)
+    assert s.get("unsupported") or ("cuDNN best" in s["what"] and s["max_err_sampled"] <= 2e-2)
+
+
+def test_layout_compare_reference_cudnn_modes():
+    for opt in (3, 6):
+        out = run("layoutCompare", "batch=4", "opt=%d" % opt, "layer=6", "iters=3")
+        s = summary(out)
+        assert s.get("unsupported") or s["max_err_sampled"] <= 1e-3
+
+
+@pytest.mark.parametrize("layout", ["NCHW", "NHWC", "CHWN"])
+def test_layout_test_driver(layout, tmp_path):
+    out = run("layoutTest", "8", "22", "128", "128", "layout=" + layout, "dir=" + str(tmp_path))
+    assert re.search(r"time [0-9.]+ us\s+[0-9.]+ TFLOPS", out)
+    assert "(ok)" in out and "moduleConv error" not in out
+    assert os.path.getsize(os.path.join(str(tmp_path), "ConvModule_%s.bin" % layout)) == 8 * 128 * 22 * 22 * 4
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2, 4])
+def test_net_test(mode):
+    out = run("netTest", "set", "batch=4", "mode=%d" % mode, "dtype=bf16", "rounds=3")
+    s = summary(out)
+    if s.get("unsupported"):
+        return
+    assert len(re.findall(r"time:[0-9.]+ ms", out)) == 3 and s["images_per_s"] > 0
