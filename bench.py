@@ -38,6 +38,7 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=256, help="images per GPU per step")
     ap.add_argument("--wino", type=int, default=0, choices=[0, 2, 4])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", action="store_true", help="after the timed region, all-gather the final outputs over NCCL once")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the cpu_baseline sample")
     return ap.parse_args()
 
@@ -254,6 +255,13 @@ def run_ours(args, rank, world, local_rank):
     L.wino_profile_read(stage_ms, stage_n)
     L.wino_profile_enable(0)
 
+    gathered = None
+    if args.gather and dist is not None:      # optional, off the timed path: the only collective of the job
+        from cudnntest_b200 import shard
+        y_all = shard.gather_outputs(stack(x_dev).clone(), args.layout, args.batch * world)
+        torch.cuda.synchronize()
+        gathered = list(y_all.shape)
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -299,6 +307,8 @@ def run_ours(args, rank, world, local_rank):
                 "d2h_bytes_per_step": y_host.numel() * y_host.element_size() * world, "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
     }
+    if gathered is not None:
+        out["gathered_output_shape"] = gathered
     if world == 1 and not args.no_cpu_baseline:
         import oracle
         oracle.build()
