@@ -250,8 +250,8 @@ def run_ours(args, rank, world, local_rank):
     import ctypes
     L.wino_profile_enable(1)
     step_resident()
-    stage_ms = (ctypes.c_float * 4)()
-    stage_n = (ctypes.c_longlong * 4)()
+    stage_ms = (ctypes.c_float * 8)()
+    stage_n = (ctypes.c_longlong * 8)()
     L.wino_profile_read(stage_ms, stage_n)
     L.wino_profile_enable(0)
 
@@ -270,33 +270,38 @@ def run_ours(args, rank, world, local_rank):
     images = args.batch * world
     value = images * args.steps / (ms * 1e-3)
     e2e_value = images * args.steps / (ms_e2e * 1e-3)
-    esize = 2 if args.dtype == "bf16" else 4
-    wino = args.wino or 4
-    a = wino + 2
-    gemm_flops = vgg.winograd_gemm_flops_per_image(wino) * args.batch
-    names = ("input_transform", "tile_gemm", "output_transform", "filter_transform")
-    stage = {n: {"ms": float(stage_ms[i]), "launches": int(stage_n[i])} for i, n in enumerate(names)}
-    # algorithmic bytes of the transform stages for the whole step (per-GPU batch)
-    ceil = lambda p_, q_: -(-p_ // q_)
-    in_bytes = sum(c * s * s * esize + a * a * ceil(s, wino) ** 2 * ceil(c, 8) * 8 * esize
-                   for (c, k, s, p) in vgg.VGG16_CONV) * args.batch
-    out_bytes = sum(a * a * ceil(s, wino) ** 2 * k * 4 + k * (s // 2 if p else s) ** 2 * esize
-                    for (c, k, s, p) in vgg.VGG16_CONV) * args.batch
-    dominant = max(range(3), key=lambda i: stage_ms[i])
-    if dominant == 1:
-        peak = peaks["tflops_sustained"] * (0.5 if args.dtype == "tf32" else 1.0)
-        achieved = gemm_flops / (stage_ms[1] * 1e-3) / 1e12
-        roofline = {"kernel": "gemm_tc_kernel" if args.dtype != "fp32" else "gemm_ffma_kernel", "bound": "tensor",
-                    "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
-                    "peak_source": peaks["source"] + " (sustained bf16 cuBLAS; halved for tf32)"}
+    # Roofline of the kernel class with the largest share of the step.  Algorithmic bytes / flops per launch set
+    # come from vgg.kernel_model (every layer's units summed per kernel class); the bound is whichever of
+    # bytes / HBM peak and flops / tensor peak is the longer time.
+    model = vgg.kernel_model(args.batch, args.dtype, args.wino or 4)
+    classes = {"input_transform": 0, "tile_gemm_plain": 1, "output_transform": 2, "tile_gemm_rowfused": 4, "direct_thin_input": 5}
+    stage = {n: {"ms": float(stage_ms[i]), "launches": int(stage_n[i])} for n, i in classes.items()}
+    dominant = max(classes, key=lambda n: stage[n]["ms"])
+    tpeak = peaks["tflops_sustained"] * (0.5 if args.dtype == "tf32" else 1.0)
+    byts, flops = model[dominant]["bytes"], model[dominant]["flops"]
+    t_meas = stage[dominant]["ms"] * 1e-3
+    t_hbm, t_tc = byts / (peaks["hbm_gbs"] * 1e9), flops / (tpeak * 1e12)
+    kernel_names = {"input_transform": "input_transform_nhwc_tma", "tile_gemm_plain": "gemm_tc_kernel" if args.dtype != "fp32" else "gemm_ffma_kernel",
+                    "output_transform": "output_transform_direct", "tile_gemm_rowfused": "gemm_tc_z_kernel",
+                    "direct_thin_input": "direct_small_c_kernel"}
+    if t_hbm >= t_tc or args.dtype == "fp32":
+        achieved = byts / t_meas / 1e9
+        roofline = {"kernel": kernel_names[dominant], "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"] + " copy bandwidth"}
     else:
-        b = in_bytes if dominant == 0 else out_bytes
-        achieved = b / (stage_ms[dominant] * 1e-3) / 1e9
-        roofline = {"kernel": names[dominant], "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
-                    "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]}
-    roofline["per_launch_ms"] = stage[names[dominant]]["ms"] / max(stage[names[dominant]]["launches"], 1)
-    roofline["stage_ms_per_step"] = {n: round(stage[n]["ms"], 4) for n in names[:3]}
-    roofline["stage_launches_per_step"] = {n: stage[n]["launches"] for n in names[:3]}
+        achieved = flops / t_meas / 1e12
+        roofline = {"kernel": kernel_names[dominant], "bound": "tensor", "achieved": achieved, "peak": tpeak, "unit": "TFLOP/s",
+                    "frac": achieved / tpeak, "traffic": None,
+                    "peak_source": peaks["source"] + " sustained bf16 cuBLAS" + (" halved for tf32" if args.dtype == "tf32" else "")}
+    roofline["algorithmic_bytes_per_step"] = byts
+    roofline["algorithmic_flops_per_step"] = flops
+    roofline["launches_per_step"] = stage[dominant]["launches"]
+    roofline["ms_per_step"] = round(stage[dominant]["ms"], 4)
+    roofline["per_class"] = {
+        n: {"ms": round(stage[n]["ms"], 4), "launches": stage[n]["launches"],
+            "hbm_frac": round(model[n]["bytes"] / max(stage[n]["ms"], 1e-9) / 1e6 / peaks["hbm_gbs"], 4),
+            "tensor_frac": round(model[n]["flops"] / max(stage[n]["ms"], 1e-9) / 1e9 / tpeak, 4)}
+        for n in classes if stage[n]["launches"]}
 
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),

@@ -209,16 +209,16 @@ int wino_profile_enable(int on) {
     return WINO_OK;
 }
 
-int wino_profile_read(float stage_ms[4], long long stage_launches[4]) {
+int wino_profile_read(float stage_ms[8], long long stage_launches[8]) {
     if (!stage_ms || !stage_launches) return fail(WINO_E_BADARG, "profile read: NULL pointer");
-    for (int i = 0; i < 4; ++i) { stage_ms[i] = 0.f; stage_launches[i] = 0; }
+    for (int i = 0; i < STAGE_COUNT; ++i) { stage_ms[i] = 0.f; stage_launches[i] = 0; }
     int rc = check_device();
     if (rc) return rc;
     WINO_CUDA_CHECK(cudaDeviceSynchronize());
     std::lock_guard<std::mutex> lock(g_prof_mutex);
     for (ProfRecord& r : g_prof) {
         float ms = 0.f;
-        if (cudaEventElapsedTime(&ms, r.start, r.stop) == cudaSuccess && r.stage >= 0 && r.stage < 4) {
+        if (cudaEventElapsedTime(&ms, r.start, r.stop) == cudaSuccess && r.stage >= 0 && r.stage < STAGE_COUNT) {
             stage_ms[r.stage] += ms;
             stage_launches[r.stage] += 1;
         }

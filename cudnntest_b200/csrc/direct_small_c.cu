@@ -231,7 +231,7 @@ int run(const DCArgs& a, cudaStream_t st) {
     const long long tiles = (a.pixels + 127) / 128;
     const long long max_ctas = 6LL * sm_count();
     dim3 grid((unsigned)(tiles < max_ctas ? tiles : max_ctas), (unsigned)((a.K + 63) / 64));
-    ProfScope prof(STAGE_GEMM, st);
+    ProfScope prof(STAGE_DIRECT, st);
     count_launch();
     direct_small_c_kernel<TIn, TOut, 3><<<grid, 128, 0, st>>>(a);
     WINO_CUDA_CHECK(cudaGetLastError());

@@ -22,6 +22,7 @@
 // too, and the CTA frees its tensor memory and returns.
 // Bound: 2*a*a*T*C*K flops against a*a*T*(Cp*s + Kq*4) bytes: C/2 flop per byte of M written, so the tensor
 // pipe bounds it only for C >= 512; below that it is bound by writing the FP32 products.
+#include <cstdlib>
 #include <mutex>
 
 #include "gemm_tc.cuh"
@@ -234,7 +235,8 @@ int launch_gemm_tc(int operand, const void* v, const void* u, float* m, int batc
     const int es = operand == OP_TF32 ? 4 : 2;
     if ((cp * es) % 16 != 0 || kq % 4 != 0) return fail(WINO_E_BADARG, "gemm_tc: row pitch must be a multiple of 16 bytes");
     if (((uintptr_t)v | (uintptr_t)u | (uintptr_t)m) & 15) return fail(WINO_E_BADARG, "gemm_tc: buffers must be 16-byte aligned");
-    const int bn = k <= 64 ? 64 : 128;
+    static const int force_bn = [] { const char* e = getenv("WINO_GEMM_BN"); return e ? atoi(e) : 0; }();
+    const int bn = force_bn ? force_bn : k <= 64 ? 64 : (k >= 256 && cp >= 512) ? 256 : 128;   // long contractions: wider tiles, fewer passes over V
     const CUtensorMapDataType dt = operand_map_type(operand);
     CUtensorMap tm_v, tm_u, tm_m;
     int rc;
@@ -249,6 +251,7 @@ int launch_gemm_tc(int operand, const void* v, const void* u, float* m, int batc
     p.idesc = make_idesc(operand, bn);
     if ((rc = status_word(&p.status))) return rc;
     const bool tf32 = operand == OP_TF32;
+    if (bn == 256) return tf32 ? run<256, true, 4>(tm_v, tm_u, tm_m, p, st) : run<256, false, 4>(tm_v, tm_u, tm_m, p, st);
     if (bn == 64) return tf32 ? run<64, true, 6>(tm_v, tm_u, tm_m, p, st) : run<64, false, 6>(tm_v, tm_u, tm_m, p, st);
     return tf32 ? run<128, true, 5>(tm_v, tm_u, tm_m, p, st) : run<128, false, 5>(tm_v, tm_u, tm_m, p, st);
 }

@@ -279,7 +279,7 @@ int run(const CUtensorMap& tm_v, const CUtensorMap& tm_u, const CUtensorMap& tm_
     WINO_CUDA_CHECK(attr_err);
     const long long total = (long long)A * p.mblocks * p.nblocks;
     const int grid = (int)(total < sm_count() ? total : sm_count());
-    ProfScope prof(STAGE_GEMM, st);
+    ProfScope prof(STAGE_GEMM_ROWFUSED, st);
     count_launch();
     gemm_tc_z_kernel<A, TF32, ZT, STAGES><<<grid, TZ_THREADS, L::TOTAL, st>>>(tm_v, tm_u, tm_z, p);
     WINO_CUDA_CHECK(cudaGetLastError());

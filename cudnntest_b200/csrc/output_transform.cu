@@ -37,28 +37,21 @@ constexpr int OT_KB = 32;
 constexpr int OT_TX = 8;
 constexpr int OT_NB = 8;
 
-// Loads the products of (tile t, filter k) and finishes the output transform, then bias, ReLU and (POOL) the 2x2
-// max.  ZF = false: the buffer holds the a*a raw products M and both 1-D transforms run here.  ZF = true: the
-// buffer holds Z = M A (a*m values, written by the row-fused tile GEMM) and only A^T along i is left.
+// Finishes the output transform of one (tile, filter) from its products held in registers, then bias, ReLU and
+// (POOL) the 2x2 max.  ZF = false: `in` holds the a*a raw products M and both 1-D transforms run here.
+// ZF = true: `in` holds Z = M A (a*m values, written by the row-fused tile GEMM) and only A^T along i is left.
 // res[p][q] holds the MO x MO stored outputs of the tile, MO = M or M/2.
-template <int A, bool POOL, bool ZF, typename TP>
-__device__ __forceinline__ void tile_outputs(const OTArgs& a, long long t, int k,
-                                             float (&res)[POOL ? (A - 2) / 2 : (A - 2)][POOL ? (A - 2) / 2 : (A - 2)]) {
+template <int A, bool POOL, bool ZF>
+__device__ __forceinline__ void finish_tile(const float (&in)[ZF ? A * (A - 2) : A * A], float b, int relu,
+                                            float (&res)[POOL ? (A - 2) / 2 : (A - 2)][POOL ? (A - 2) / 2 : (A - 2)]) {
     constexpr int M = A - 2;
     float y[M][M];
-    const long long plane = a.tp * a.kq;
-    const TP* src = reinterpret_cast<const TP*>(a.m) + t * a.kq + k;
     if constexpr (ZF) {
-        float z[A][M];
-#pragma unroll
-        for (int i = 0; i < A; ++i)
-#pragma unroll
-            for (int q = 0; q < M; ++q) z[i][q] = to_float<TP>(src[(long long)(i * M + q) * plane]);
 #pragma unroll
         for (int q = 0; q < M; ++q) {
             float col[A], out[M];
 #pragma unroll
-            for (int i = 0; i < A; ++i) col[i] = z[i][q];
+            for (int i = 0; i < A; ++i) col[i] = in[i * M + q];
             at_1d<A>(col, out);
 #pragma unroll
             for (int p = 0; p < M; ++p) y[p][q] = out[p];
@@ -68,16 +61,15 @@ __device__ __forceinline__ void tile_outputs(const OTArgs& a, long long t, int k
 #pragma unroll
         for (int i = 0; i < A; ++i)
 #pragma unroll
-            for (int j = 0; j < A; ++j) mm[i][j] = to_float<TP>(src[(long long)(i * A + j) * plane]);
+            for (int j = 0; j < A; ++j) mm[i][j] = in[i * A + j];
         output_tile_transform<A>(mm, y);
     }
-    const float b = a.bias ? __ldg(a.bias + k) : 0.f;
 #pragma unroll
     for (int p = 0; p < M; ++p)
 #pragma unroll
         for (int q = 0; q < M; ++q) {
             float v = y[p][q] + b;
-            if (a.relu) v = fmaxf(v, 0.f);
+            if (relu) v = fmaxf(v, 0.f);
             y[p][q] = v;
         }
     if constexpr (POOL) {
@@ -91,6 +83,78 @@ __device__ __forceinline__ void tile_outputs(const OTArgs& a, long long t, int k
         for (int p = 0; p < M; ++p)
 #pragma unroll
             for (int q = 0; q < M; ++q) res[p][q] = y[p][q];
+    }
+}
+
+// one (tile t, filter k): scalar loads, lanes along k
+template <int A, bool POOL, bool ZF, typename TP>
+__device__ __forceinline__ void tile_outputs(const OTArgs& a, long long t, int k,
+                                             float (&res)[POOL ? (A - 2) / 2 : (A - 2)][POOL ? (A - 2) / 2 : (A - 2)]) {
+    constexpr int P = ZF ? A * (A - 2) : A * A;
+    float in[P];
+    const long long plane = a.tp * a.kq;
+    const TP* src = reinterpret_cast<const TP*>(a.m) + t * a.kq + k;
+#pragma unroll
+    for (int i = 0; i < P; ++i) in[i] = to_float<TP>(src[(long long)i * plane]);
+    finish_tile<A, POOL, ZF>(in, a.bias ? __ldg(a.bias + k) : 0.f, a.relu, res);
+}
+
+template <typename TP>
+__device__ __forceinline__ float2 load_pair(const TP* p);
+template <>
+__device__ __forceinline__ float2 load_pair<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <>
+__device__ __forceinline__ float2 load_pair<__half>(const __half* p) { return __half22float2(*reinterpret_cast<const __half2*>(p)); }
+
+template <typename T>
+__device__ __forceinline__ void store_pair(T* p, float a, float b);
+template <>
+__device__ __forceinline__ void store_pair<float>(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+template <>
+__device__ __forceinline__ void store_pair<__nv_bfloat16>(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+// NHWC destination, two adjacent filters per thread (K even): every warp-wide load covers a full 128-byte (half
+// products) or 256-byte (float products) row segment and every store a full 128 / 256-byte segment of y.
+template <int A, bool POOL, bool ZF, typename TP, typename TOut>
+__global__ void __launch_bounds__(256) output_transform_direct_x2(OTArgs a, long long T) {
+    constexpr int MO = POOL ? (A - 2) / 2 : (A - 2);
+    constexpr int P = ZF ? A * (A - 2) : A * A;
+    const int kpairs = (a.K + 1) / 2;
+    const int kspan = (kpairs + 31) / 32 * 32;
+    const long long item = (long long)blockIdx.x * 256 + threadIdx.x;
+    const int k = (int)(item % kspan) * 2;
+    const long long t = item / kspan;
+    if (t >= T || k >= a.K) return;
+    float in0[P], in1[P];
+    const long long plane = a.tp * a.kq;
+    const TP* src = reinterpret_cast<const TP*>(a.m) + t * a.kq + k;
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+        const float2 v = load_pair<TP>(src + (long long)i * plane);
+        in0[i] = v.x;
+        in1[i] = v.y;
+    }
+    float r0[MO][MO], r1[MO][MO];
+    float b0 = 0.f, b1 = 0.f;
+    if (a.bias) { b0 = __ldg(a.bias + k); b1 = __ldg(a.bias + k + 1); }
+    finish_tile<A, POOL, ZF>(in0, b0, a.relu, r0);
+    finish_tile<A, POOL, ZF>(in1, b1, a.relu, r1);
+    const int tiles_img = a.bny * a.bnx;
+    const int n = a.n0 + (int)(t / tiles_img);
+    const int rem = (int)(t % tiles_img);
+    const int by = rem / a.bnx, bx = rem % a.bnx;
+    TOut* __restrict__ y = (TOut*)a.y + (long long)n * a.sy.n + k;
+#pragma unroll
+    for (int p = 0; p < MO; ++p) {
+        const int oy = by * MO + p;
+        if (oy >= a.ph) continue;
+#pragma unroll
+        for (int q = 0; q < MO; ++q) {
+            const int ox = bx * MO + q;
+            if (ox < a.pw) store_pair<TOut>(y + oy * a.sy.h + ox * a.sy.w, r0[p][q], r1[p][q]);
+        }
     }
 }
 
@@ -207,7 +271,11 @@ static int run(const wino_conv_desc& d, const Geometry& g, const OTArgs& a, cuda
     const int kchunks = (d.k + OT_KB - 1) / OT_KB;
     ProfScope prof(STAGE_OUTPUT, st);
     count_launch();
-    if (d.layout_out == WINO_NHWC) {
+    if (d.layout_out == WINO_NHWC && d.k % 2 == 0 && ((uintptr_t)a.m & 7) == 0 && ((uintptr_t)a.y & 7) == 0) {
+        const long long T = (long long)a.ns * g.tiles_img;
+        const long long items = T * (((d.k / 2) + 31) / 32 * 32);
+        output_transform_direct_x2<A, POOL, ZF, TP, TOut><<<(unsigned)((items + 255) / 256), 256, 0, st>>>(a, T);
+    } else if (d.layout_out == WINO_NHWC) {
         const long long T = (long long)a.ns * g.tiles_img;
         const long long items = T * kchunks * OT_KB;
         output_transform_direct<A, POOL, ZF, TP, TOut><<<(unsigned)((items + 255) / 256), 256, 0, st>>>(a, T);

@@ -134,11 +134,12 @@ int wino_maxpool2x2(int layout, int n, int c, int h, int w, int dtype, const voi
  * wino_profile_enable(1): from now on every kernel launched by wino_conv_forward / wino_filter_transform is
  * bracketed by a pair of CUDA events on its own stream (takes the role of the commented-out five-event
  * per-stage breakdown of comparison/wrapedConv_NCHW.cuh:88-138).  wino_profile_read synchronises the
- * device, adds up the elapsed milliseconds and launches per stage since the last read (index 0 input
- * transform, 1 tile GEMM, 2 output transform, 3 filter transform) and clears the record. */
+ * device, adds up the elapsed milliseconds and launches per kernel class since the last read (index 0 input
+ * transform, 1 plain tile GEMM (tensor-core or FFMA), 2 output transform, 3 filter transform, 4 row-fused
+ * tile GEMM, 5 thin-input direct convolution, 6-7 unused) and clears the record. */
 long long wino_launch_count(void);
 int wino_profile_enable(int on);
-int wino_profile_read(float stage_ms[4], long long stage_launches[4]);
+int wino_profile_read(float stage_ms[8], long long stage_launches[8]);
 
 /* ---- stage-level entry points (tests, profiling) --------------------------------------------------
  * Buffers for a slab of `ns` images starting at image n0 (T = ns*bny*bnx tiles, bny = ceil((h+2p-2)/m)):
