@@ -36,6 +36,7 @@ struct DCArgs {
     int oh, ow;
     long long pixels;      // N * oh * ow
     int relu;
+    int n_fastest;         // pixel order of a tile: images fastest (CHWN) or columns fastest
     uint32_t idesc;
     Strides sx, sw, sy;
     int* status;
@@ -119,10 +120,17 @@ __global__ void __launch_bounds__(128) direct_small_c_kernel(const DCArgs a) {
         const bool valid = p < a.pixels;
         int n = 0, oy = 0, ox = 0;
         if (valid) {
-            ox = (int)(p % a.ow);
-            const long long q = p / a.ow;
-            oy = (int)(q % a.oh);
-            n = (int)(q / a.oh);
+            if (a.n_fastest) {          // CHWN: consecutive threads take consecutive images of one output position
+                n = (int)(p % a.N);
+                const long long q = p / a.N;
+                ox = (int)(q % a.ow);
+                oy = (int)(q / a.ow);
+            } else {
+                ox = (int)(p % a.ow);
+                const long long q = p / a.ow;
+                oy = (int)(q % a.oh);
+                n = (int)(q / a.oh);
+            }
         }
         {
             float v[32];
@@ -269,6 +277,7 @@ int launch_direct_small_c(const wino_conv_desc& d, const Geometry& g, const void
     a.oh = g.oh; a.ow = g.ow;
     a.pixels = (long long)d.n * g.oh * g.ow;
     a.relu = d.relu;
+    a.n_fastest = d.layout_in == WINO_CHWN || d.layout_out == WINO_CHWN;
     a.idesc = make_idesc(d.dtype == WINO_TF32 ? OP_TF32 : OP_BF16, 64);
     a.sx = act_strides(d.layout_in, d.n, d.c, d.h, d.w);
     a.sw = filter_strides(d.layout_in, d.k, d.c);   // unused by the kernel: the filters arrive packed

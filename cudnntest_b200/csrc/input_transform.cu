@@ -4,17 +4,19 @@
 // (comparison/wrapedConv_NCHW.cuh:760-856, wrapedConv_NHWC.cuh:266-329, wrapedConv_CHWN.cuh:225-275),
 // which map one thread to one (tile, channel) and issue a*a scalar stores at plane stride.
 //
-// Design: every layout writes the same operand buffer V[xi][tile][Cp] (channels contiguous = the
-// K-major operand the tile GEMM wants), so the layouts differ only in how a CTA stages its input
-// patch in shared memory:
-//   * NHWC, NCHW ("strip"): a CTA owns TX horizontally adjacent tiles x 32 channels of one image row
-//     of tiles; it stages the a x (m*TX+2) x 32 halo patch once (the horizontal halo is read once, not
-//     1.5x), with global loads coalesced along c (NHWC) or along w (NCHW); zero padding is the loader's
-//     predicate.
-//   * CHWN ("batch"): a CTA owns one tile position x 8 images x 32 channels, loads coalesced along n.
-// Shared memory is [position][channel] with a row pitch chosen so that both the layout's load order
-// and the transform's read order (lanes along c) are bank-conflict free.  Then each thread transforms
-// one (tile, channel) patch in registers and the warp stores 32 consecutive channels per (xi, tile).
+// Every layout writes the same operand buffer V[xi][tile][Cp] (channels contiguous = the K-major operand the
+// tile GEMM wants), so the layouts differ only in how a CTA stages its input patch in shared memory.  The
+// staged patch is an array of 128-byte rows, one row per spatial position, holding 32 4-byte "words" of
+// channel data (two bf16 channels or one float channel per word).  The transform step is the same everywhere:
+// warp w owns tile w of the unit, lane l owns word l; shared-memory reads are conflict free and every global
+// store instruction writes one full 128-byte line of V.
+//   * NHWC, pixel pitch a multiple of 16 bytes: persistent CTAs, the a x (8m+2) x 128-byte halo patch of 8
+//     adjacent tiles arrives by ONE 4-D cp.async.bulk.tensor load into a 3-deep ring; rows, columns and channels
+//     outside the tensor are zero filled by the TMA unit (= the zero padding and the Cp padding of V);
+//   * NCHW: the same unit, loaded with 16-byte vectors along w (aligned chunks that cover the halo row) and
+//     scattered into the word rows; lanes run along channels so the scatter is conflict free;
+//   * CHWN: unit = one tile position x 8 images x 128 bytes of channels, loaded with 16-byte vectors along n;
+//   * NHWC with an unaligned pixel pitch (C = 3, 20, ...): scalar loads, lanes along channels.
 // HBM bound: reads N*C*H*W elements (x ~1.5 through L2 for the vertical halo), writes a*a*T*Cp.
 #include <cstdlib>
 #include <mutex>
@@ -24,12 +26,6 @@
 #include "wino_math.cuh"
 
 namespace wino {
-
-// WINO_GENERIC_TRANSFORMS=1 routes every layout through the generic staged kernels (testing aid)
-static bool force_generic() {
-    static const bool v = [] { const char* e = getenv("WINO_GENERIC_TRANSFORMS"); return e && e[0] == '1'; }();
-    return v;
-}
 
 struct ITArgs {
     const void* x;
@@ -42,122 +38,10 @@ struct ITArgs {
     Strides sx;
 };
 
-constexpr int IT_CB = 32;   // channels per CTA
-constexpr int IT_TX = 8;    // tiles per CTA along x (strip mode)
-constexpr int IT_NB = 8;    // images per CTA (batch mode)
+constexpr int IT_TX = 8;    // tiles per unit along x (NHWC, NCHW)
+constexpr int IT_NB = 8;    // images per unit (CHWN)
 
-template <int A, typename TOp>
-__device__ __forceinline__ void transform_and_store(const float* patch, int pos_stride_r, int pos_stride_s, int pitch,
-                                                    int c_l, TOp* __restrict__ v, long long tp, int cp, long long t,
-                                                    int c) {
-    float d[A][A], o[A][A];
-#pragma unroll
-    for (int r = 0; r < A; ++r)
-#pragma unroll
-        for (int s = 0; s < A; ++s) d[r][s] = patch[(r * pos_stride_r + s * pos_stride_s) * pitch + c_l];
-    input_tile_transform<A>(d, o);
-    const long long plane = tp * cp;
-    TOp* dst = v + t * cp + c;
-#pragma unroll
-    for (int i = 0; i < A; ++i)
-#pragma unroll
-        for (int j = 0; j < A; ++j) dst[(long long)(i * A + j) * plane] = from_float<TOp>(o[i][j]);
-}
-
-// strip mode: NHWC (W_FASTEST = false) and NCHW (W_FASTEST = true)
-template <int A, bool W_FASTEST, typename TIn, typename TOp>
-__global__ void __launch_bounds__(256) input_transform_strip(ITArgs a) {
-    constexpr int M = A - 2;
-    constexpr int COLS = M * IT_TX + 2;
-    constexpr int PITCH = IT_CB + 1;
-    __shared__ float patch[A * COLS * PITCH];
-
-    const int cchunks = (a.cp + IT_CB - 1) / IT_CB;
-    const int c0 = (blockIdx.x % cchunks) * IT_CB;
-    const int bx0 = (blockIdx.x / cchunks) * IT_TX;
-    const int by = blockIdx.y;
-    const int n = a.n0 + blockIdx.z;
-    const int gh0 = by * M - a.pad, gw0 = bx0 * M - a.pad;
-    const TIn* __restrict__ x = (const TIn*)a.x + (long long)n * a.sx.n;
-
-    for (int idx = threadIdx.x; idx < A * COLS * IT_CB; idx += 256) {
-        int c_l, col, r;
-        if (W_FASTEST) {
-            col = idx % COLS;
-            const int rc = idx / COLS;
-            c_l = rc % IT_CB;
-            r = rc / IT_CB;
-        } else {
-            c_l = idx % IT_CB;
-            const int rc = idx / IT_CB;
-            col = rc % COLS;
-            r = rc / COLS;
-        }
-        const int gh = gh0 + r, gw = gw0 + col, c = c0 + c_l;
-        float val = 0.f;
-        if (gh >= 0 && gh < a.H && gw >= 0 && gw < a.W && c < a.C)
-            val = to_float<TIn>(x[c * a.sx.c + gh * a.sx.h + gw * a.sx.w]);
-        patch[(r * COLS + col) * PITCH + c_l] = val;
-    }
-    __syncthreads();
-
-    const int item = threadIdx.x;  // IT_TX * IT_CB == 256
-    const int c_l = item % IT_CB, tl = item / IT_CB;
-    const int bx = bx0 + tl, c = c0 + c_l;
-    if (bx < a.bnx && c < a.cp) {
-        const long long t = ((long long)blockIdx.z * a.bny + by) * a.bnx + bx;
-        transform_and_store<A, TOp>(patch + tl * M * PITCH, COLS, 1, PITCH, c_l, (TOp*)a.v, a.tp, a.cp, t, c);
-    }
-}
-
-// batch mode: CHWN
-template <int A, typename TIn, typename TOp>
-__global__ void __launch_bounds__(256) input_transform_batch(ITArgs a) {
-    constexpr int M = A - 2;
-    constexpr int PITCH = IT_CB + 4;  // lanes (n_l, c_l) -> bank 4*n_l + c_l on store, c_l on load
-    __shared__ float patch[A * A * IT_NB * PITCH];
-
-    const int cchunks = (a.cp + IT_CB - 1) / IT_CB;
-    const int c0 = (blockIdx.x % cchunks) * IT_CB;
-    const int nb0 = (blockIdx.x / cchunks) * IT_NB;
-    const int bx = blockIdx.y, by = blockIdx.z;
-    const int gh0 = by * M - a.pad, gw0 = bx * M - a.pad;
-    const TIn* __restrict__ x = (const TIn*)a.x;
-
-    for (int idx = threadIdx.x; idx < A * A * IT_NB * IT_CB; idx += 256) {
-        const int n_l = idx % IT_NB;
-        const int rc = idx / IT_NB;
-        const int c_l = rc % IT_CB;
-        const int rs = rc / IT_CB;
-        const int gh = gh0 + rs / A, gw = gw0 + rs % A, c = c0 + c_l;
-        float val = 0.f;
-        if (gh >= 0 && gh < a.H && gw >= 0 && gw < a.W && c < a.C && nb0 + n_l < a.ns)
-            val = to_float<TIn>(x[(long long)(a.n0 + nb0 + n_l) * a.sx.n + c * a.sx.c + gh * a.sx.h + gw * a.sx.w]);
-        patch[(rs * IT_NB + n_l) * PITCH + c_l] = val;
-    }
-    __syncthreads();
-
-    const int item = threadIdx.x;  // IT_NB * IT_CB == 256
-    const int c_l = item % IT_CB, n_l = item / IT_CB;
-    const int c = c0 + c_l;
-    if (nb0 + n_l < a.ns && c < a.cp) {
-        const long long t = ((long long)(nb0 + n_l) * a.bny + by) * a.bnx + bx;
-        transform_and_store<A, TOp>(patch + n_l * PITCH, A * IT_NB, IT_NB, PITCH, c_l, (TOp*)a.v, a.tp, a.cp, t, c);
-    }
-}
-
-// ---- NHWC fast path: TMA-staged, persistent ---------------------------------------------------------
-// Used when the pixel pitch C*sizeof(T) is a multiple of 16 bytes (TMA's stride rule).  A CTA walks work
-// units (image, tile row, 8 adjacent tiles, 128 bytes of channels) round-robin; one elected thread brings
-// each unit's a x (8m+2) x 128-byte halo patch into a 3-deep shared-memory ring with a single 4-D
-// cp.async.bulk.tensor load whose out-of-range rows, columns and channels are zero filled by the TMA unit
-// (= the convolution's zero padding and the Cp padding of V, with no predicates in the kernel).  Warp w owns
-// tile w of the unit, lane l owns the l-th 4-byte word of the 128-byte channel chunk (two bf16 or one float
-// channel): shared-memory reads are conflict free and every global store instruction writes one full 128-byte
-// line of V.
-constexpr int ITT_STAGES = 3;
-constexpr int ITT_WAIT_CODE = 5;
-
+// ---- word <-> float conversion ------------------------------------------------------------------------
 template <typename TIn, typename TOp>
 struct WordIO;
 template <typename TOp>
@@ -187,14 +71,175 @@ struct WordIO<__nv_bfloat16, __half> {
     }
 };
 
+// Transforms the a x a patch whose words sit at src[(r*row_stride + s*col_stride) * 32] and stores the a*a
+// results as words at dst[xi * plane_words].
+// SWZ: the word of lane l for patch element (r, q) sits at column l ^ (r*A + q) of its row (CHWN staging).
+template <int A, typename TIn, typename TOp, bool SWZ = false>
+__device__ __forceinline__ void transform_words(const uint32_t* src, int row_stride, int col_stride, uint32_t* dst,
+                                                long long plane_words, int lane = 0) {
+    using IO = WordIO<TIn, TOp>;
+    uint32_t w[A][A];
+#pragma unroll
+    for (int r = 0; r < A; ++r)
+#pragma unroll
+        for (int q = 0; q < A; ++q)
+            w[r][q] = src[(r * row_stride + q * col_stride) * 32 + (SWZ ? (lane ^ ((r * A + q) & 31)) : 0)];
+    float d[A][A], lo[A][A], hi[A][A];
+#pragma unroll
+    for (int r = 0; r < A; ++r)
+#pragma unroll
+        for (int q = 0; q < A; ++q) d[r][q] = IO::get(w[r][q], 0);
+    input_tile_transform<A>(d, lo);
+    if (IO::VEC == 2) {
+#pragma unroll
+        for (int r = 0; r < A; ++r)
+#pragma unroll
+            for (int q = 0; q < A; ++q) d[r][q] = IO::get(w[r][q], 1);
+        input_tile_transform<A>(d, hi);
+    }
+#pragma unroll
+    for (int r = 0; r < A; ++r)
+#pragma unroll
+        for (int q = 0; q < A; ++q) dst[(long long)(r * A + q) * plane_words] = IO::put(lo[r][q], IO::VEC == 2 ? hi[r][q] : 0.f);
+}
+
+// writes element (channel c_l of the unit) of spatial position `pos` into the staged word rows
+template <typename TIn>
+__device__ __forceinline__ void put_element(uint8_t* patch, int pos, int c_l, TIn v) {
+    reinterpret_cast<TIn*>(patch + pos * 128)[c_l] = v;
+}
+
+// ---- NHWC (unaligned pitch), NCHW: strip unit, cooperative loads ---------------------------------------
+template <int A, bool NCHW_IN, typename TIn, typename TOp>
+__global__ void __launch_bounds__(256, 2) input_transform_strip(const ITArgs a, const int bxchunks, const int cchunks) {
+    constexpr int M = A - 2;
+    constexpr int COLS = M * IT_TX + 2;
+    constexpr int VEC = 4 / (int)sizeof(TIn);
+    constexpr int CH = 32 * VEC;                   // channels per unit
+    constexpr int VE = 16 / (int)sizeof(TIn);      // elements per 16-byte vector
+    __shared__ __align__(16) uint8_t patch[A * COLS * 128];
+
+    const int c0 = (blockIdx.x % cchunks) * CH;
+    const int bx0 = (blockIdx.x / cchunks) * IT_TX;
+    const int by = blockIdx.y;
+    const int n = a.n0 + blockIdx.z;
+    const int gh0 = by * M - a.pad, gw0 = bx0 * M - a.pad;
+    const TIn* __restrict__ x = reinterpret_cast<const TIn*>(a.x) + (long long)n * a.sx.n;
+    const TIn zero = from_float<TIn>(0.f);
+
+    if (NCHW_IN) {
+        // aligned 16-byte chunks along w that cover columns [gw0, gw0 + COLS); lanes run along channels
+        const int ws = (gw0 >= 0 ? gw0 / VE : -((-gw0 + VE - 1) / VE)) * VE;
+        const int off = gw0 - ws;                                  // 0 .. VE-1
+        const int nchunks = (off + COLS + VE - 1) / VE;
+        const bool vec_ok = (a.W % VE) == 0 && ((a.sx.n | a.sx.c) % VE) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0;
+        for (int item = threadIdx.x; item < CH * A * nchunks; item += 256) {
+            const int c_l = item % CH;
+            const int rc = item / CH;
+            const int r = rc % A, chunk = rc / A;
+            const int gh = gh0 + r, gw = ws + chunk * VE, c = c0 + c_l;
+            __align__(16) TIn vals[VE];
+            const bool row_ok = gh >= 0 && gh < a.H && c < a.C;
+            if (row_ok && vec_ok && gw >= 0 && gw + VE <= a.W) {
+                *reinterpret_cast<uint4*>(vals) = *reinterpret_cast<const uint4*>(x + c * a.sx.c + gh * a.sx.h + gw);
+            } else {
+#pragma unroll
+                for (int e = 0; e < VE; ++e) {
+                    const int w = gw + e;
+                    vals[e] = (row_ok && w >= 0 && w < a.W) ? x[c * a.sx.c + gh * a.sx.h + w] : zero;
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < VE; ++e) {
+                const int col = chunk * VE + e - off;
+                if (col >= 0 && col < COLS) put_element<TIn>(patch, r * COLS + col, c_l, vals[e]);
+            }
+        }
+    } else {
+        for (int item = threadIdx.x; item < A * COLS * CH; item += 256) {
+            const int c_l = item % CH;
+            const int rc = item / CH;
+            const int col = rc % COLS, r = rc / COLS;
+            const int gh = gh0 + r, gw = gw0 + col, c = c0 + c_l;
+            TIn val = zero;
+            if (gh >= 0 && gh < a.H && gw >= 0 && gw < a.W && c < a.C) val = x[c * a.sx.c + gh * a.sx.h + gw * a.sx.w];
+            put_element<TIn>(patch, r * COLS + col, c_l, val);
+        }
+    }
+    __syncthreads();
+
+    const int tl = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int bx = bx0 + tl, c = c0 + lane * VEC;
+    if (bx < a.bnx && c < a.cp) {
+        const long long t = ((long long)blockIdx.z * a.bny + by) * a.bnx + bx;
+        transform_words<A, TIn, TOp>(reinterpret_cast<const uint32_t*>(patch) + (tl * M) * 32 + lane, COLS, 1,
+                                     reinterpret_cast<uint32_t*>(a.v) + (t * a.cp + c) / VEC, a.tp * a.cp / VEC);
+    }
+}
+
+// ---- CHWN: batch unit (one tile position, 8 images), 16-byte loads along n ---------------------------------
+template <int A, typename TIn, typename TOp>
+__global__ void __launch_bounds__(256, 2) input_transform_batch(const ITArgs a, const int cchunks) {
+    constexpr int M = A - 2;
+    constexpr int VEC = 4 / (int)sizeof(TIn);
+    constexpr int CH = 32 * VEC;
+    constexpr int VE = 16 / (int)sizeof(TIn);      // images per 16-byte vector: 8 (bf16) or 4 (float)
+    constexpr int NV = IT_NB / VE;                 // vectors per 8 images
+    __shared__ __align__(16) uint8_t patch[A * A * IT_NB * 128];
+
+    const int c0 = (blockIdx.x % cchunks) * CH;
+    const int nb0 = (blockIdx.x / cchunks) * IT_NB;
+    const int bx = blockIdx.y, by = blockIdx.z;
+    const int gh0 = by * M - a.pad, gw0 = bx * M - a.pad;
+    const TIn* __restrict__ x = reinterpret_cast<const TIn*>(a.x);
+    const TIn zero = from_float<TIn>(0.f);
+    const int nbase = a.n0 + nb0;
+    // sx.n == 1: images are contiguous; a vector of VE images is aligned when every stride and the base are
+    const bool vec_ok = ((a.sx.c | a.sx.h | a.sx.w) % VE) == 0 && (nbase % VE) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0;
+
+    // lanes run over the a*a patch positions of ONE channel (addresses inside one channel plane); the word column
+    // is XOR-swizzled with the position so that this scatter and the transform's reads are both conflict free
+    for (int item = threadIdx.x; item < CH * A * A * NV; item += 256) {
+        const int rs = item % (A * A);
+        const int rc = item / (A * A);
+        const int nv = rc % NV, c_l = rc / NV;
+        const int gh = gh0 + rs / A, gw = gw0 + rs % A, c = c0 + c_l;
+        const int n_l0 = nv * VE;
+        __align__(16) TIn vals[VE];
+        const bool ok = gh >= 0 && gh < a.H && gw >= 0 && gw < a.W && c < a.C;
+        const TIn* src = x + c * a.sx.c + gh * a.sx.h + gw * a.sx.w + (nbase + n_l0);
+        if (ok && vec_ok && nb0 + n_l0 + VE <= a.ns) {
+            *reinterpret_cast<uint4*>(vals) = *reinterpret_cast<const uint4*>(src);
+        } else {
+#pragma unroll
+            for (int e = 0; e < VE; ++e) vals[e] = (ok && nb0 + n_l0 + e < a.ns) ? src[e] : zero;
+        }
+        const int word = (c_l / VEC) ^ (rs & 31);
+#pragma unroll
+        for (int e = 0; e < VE; ++e) put_element<TIn>(patch, rs * IT_NB + n_l0 + e, word * VEC + (c_l % VEC), vals[e]);
+    }
+    __syncthreads();
+
+    const int n_l = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int c = c0 + lane * VEC;
+    if (nb0 + n_l < a.ns && c < a.cp) {
+        const long long t = ((long long)(nb0 + n_l) * a.bny + by) * a.bnx + bx;
+        transform_words<A, TIn, TOp, true>(reinterpret_cast<const uint32_t*>(patch) + n_l * 32, A * IT_NB, IT_NB,
+                                           reinterpret_cast<uint32_t*>(a.v) + (t * a.cp + c) / VEC, a.tp * a.cp / VEC, lane);
+    }
+}
+
+// ---- NHWC, aligned pitch: TMA-staged, persistent ------------------------------------------------------------
+constexpr int ITT_STAGES = 3;
+constexpr int ITT_WAIT_CODE = 5;
+
 template <int A, typename TIn, typename TOp>
 __global__ void __launch_bounds__(256, 2)
 input_transform_nhwc_tma(const __grid_constant__ CUtensorMap tm_x, const ITArgs a, const int bxchunks, const int cchunks,
                          const long long units, int* status) {
-    using IO = WordIO<TIn, TOp>;
     constexpr int M = A - 2;
     constexpr int COLS = M * IT_TX + 2;
-    constexpr int VEC = IO::VEC;
+    constexpr int VEC = 4 / (int)sizeof(TIn);
     constexpr int CH = 32 * VEC;                       // channels per unit (128 bytes)
     constexpr int STAGE_BYTES = A * COLS * 128;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -241,35 +286,19 @@ input_transform_nhwc_tma(const __grid_constant__ CUtensorMap tm_x, const ITArgs 
         decode(i, n_l, by, bx0, c0);
         const int bx = bx0 + tl, c = c0 + lane * VEC;
         if (bx < a.bnx && c < a.cp) {
-            const uint32_t* src = reinterpret_cast<const uint32_t*>(smem + s * STAGE_BYTES) + (tl * M) * 32 + lane;
-            uint32_t w[A][A];
-#pragma unroll
-            for (int r = 0; r < A; ++r)
-#pragma unroll
-                for (int q = 0; q < A; ++q) w[r][q] = src[(r * COLS + q) * 32];
-            float d[A][A], lo[A][A], hi[A][A];
-#pragma unroll
-            for (int r = 0; r < A; ++r)
-#pragma unroll
-                for (int q = 0; q < A; ++q) d[r][q] = IO::get(w[r][q], 0);
-            input_tile_transform<A>(d, lo);
-            if (VEC == 2) {
-#pragma unroll
-                for (int r = 0; r < A; ++r)
-#pragma unroll
-                    for (int q = 0; q < A; ++q) d[r][q] = IO::get(w[r][q], 1);
-                input_tile_transform<A>(d, hi);
-            }
             const long long t = ((long long)n_l * a.bny + by) * a.bnx + bx;
-            uint32_t* dst = vw + (t * a.cp + c) / VEC;
-#pragma unroll
-            for (int r = 0; r < A; ++r)
-#pragma unroll
-                for (int q = 0; q < A; ++q) dst[(long long)(r * A + q) * plane_words] = IO::put(lo[r][q], VEC == 2 ? hi[r][q] : 0.f);
+            transform_words<A, TIn, TOp>(reinterpret_cast<const uint32_t*>(smem + s * STAGE_BYTES) + (tl * M) * 32 + lane, COLS, 1,
+                                         vw + (t * a.cp + c) / VEC, plane_words);
         }
         __syncthreads();   // the slot is free for the load issued at the top of the next iteration
     }
     if (aborted && threadIdx.x == 0) drain_after_abort();
+}
+
+// WINO_GENERIC_TRANSFORMS=1 keeps NHWC off the TMA path (testing aid)
+static bool force_generic() {
+    static const bool v = [] { const char* e = getenv("WINO_GENERIC_TRANSFORMS"); return e && e[0] == '1'; }();
+    return v;
 }
 
 template <int A, typename TIn, typename TOp>
@@ -312,21 +341,22 @@ static int run_nhwc_tma(const wino_conv_desc& d, const Geometry& g, const ITArgs
 
 template <int A, typename TIn, typename TOp>
 static int run(const wino_conv_desc& d, const Geometry& g, const ITArgs& a, cudaStream_t st) {
-    static_assert(IT_TX * IT_CB == 256 && IT_NB * IT_CB == 256, "one work item per thread");
+    constexpr int CH = 32 * (4 / (int)sizeof(TIn));
     if (d.layout_in == WINO_NHWC && (d.c * sizeof(TIn)) % 16 == 0 && ((uintptr_t)a.x & 15) == 0 && !force_generic())
         return run_nhwc_tma<A, TIn, TOp>(d, g, a, st);
-    const int cchunks = (g.cp + IT_CB - 1) / IT_CB;
+    const int cchunks = (g.cp + CH - 1) / CH;
     ProfScope prof(STAGE_INPUT, st);
     count_launch();
     if (d.layout_in == WINO_CHWN) {
         dim3 grid((unsigned)(((a.ns + IT_NB - 1) / IT_NB) * cchunks), (unsigned)g.bnx, (unsigned)g.bny);
-        input_transform_batch<A, TIn, TOp><<<grid, 256, 0, st>>>(a);
+        input_transform_batch<A, TIn, TOp><<<grid, 256, 0, st>>>(a, cchunks);
     } else {
-        dim3 grid((unsigned)(((g.bnx + IT_TX - 1) / IT_TX) * cchunks), (unsigned)g.bny, (unsigned)a.ns);
+        const int bxchunks = (g.bnx + IT_TX - 1) / IT_TX;
+        dim3 grid((unsigned)(bxchunks * cchunks), (unsigned)g.bny, (unsigned)a.ns);
         if (d.layout_in == WINO_NCHW)
-            input_transform_strip<A, true, TIn, TOp><<<grid, 256, 0, st>>>(a);
+            input_transform_strip<A, true, TIn, TOp><<<grid, 256, 0, st>>>(a, bxchunks, cchunks);
         else
-            input_transform_strip<A, false, TIn, TOp><<<grid, 256, 0, st>>>(a);
+            input_transform_strip<A, false, TIn, TOp><<<grid, 256, 0, st>>>(a, bxchunks, cchunks);
     }
     WINO_CUDA_CHECK(cudaGetLastError());
     return WINO_OK;

@@ -186,89 +186,164 @@ __global__ void __launch_bounds__(256) output_transform_direct(OTArgs a, long lo
     }
 }
 
-// NCHW destination: stage TX tiles x 32 filters, store rows contiguous along w
+// packs VE consecutive outputs into one 16-byte vector
+template <typename TOut>
+__device__ __forceinline__ uint4 pack16(const float* v);
+template <>
+__device__ __forceinline__ uint4 pack16<float>(const float* v) {
+    return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+}
+template <>
+__device__ __forceinline__ uint4 pack16<__nv_bfloat16>(const float* v) {
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+        w[e] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Transform step shared by the NCHW and CHWN kernels: the thread loads the products of two adjacent filters
+// (k, k+1) of tile t — always inside the Kq-padded rows — and leaves the MO x MO outputs of both in the staging
+// array at [pos(p, q)][k_l], [pos][k_l + 1].
+template <int A, bool POOL, bool ZF, typename TP, typename PosFn>
+__device__ __forceinline__ void stage_pair(const OTArgs& a, long long t, int k, int k_l, float* stage, int pitch, PosFn pos) {
+    constexpr int MO = POOL ? (A - 2) / 2 : (A - 2);
+    constexpr int P = ZF ? A * (A - 2) : A * A;
+    float in0[P], in1[P];
+    const long long plane = a.tp * a.kq;
+    const TP* src = reinterpret_cast<const TP*>(a.m) + t * a.kq + k;
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+        const float2 v = load_pair<TP>(src + (long long)i * plane);
+        in0[i] = v.x;
+        in1[i] = v.y;
+    }
+    float r0[MO][MO], r1[MO][MO];
+    float b0 = 0.f, b1 = 0.f;
+    if (a.bias) {
+        b0 = k < a.K ? __ldg(a.bias + k) : 0.f;
+        b1 = k + 1 < a.K ? __ldg(a.bias + k + 1) : 0.f;
+    }
+    finish_tile<A, POOL, ZF>(in0, b0, a.relu, r0);
+    finish_tile<A, POOL, ZF>(in1, b1, a.relu, r1);
+#pragma unroll
+    for (int p = 0; p < MO; ++p)
+#pragma unroll
+        for (int q = 0; q < MO; ++q) {
+            float* dst = stage + pos(p, q) * pitch + k_l;
+            dst[0] = r0[p][q];
+            dst[1] = r1[p][q];
+        }
+}
+
+constexpr int OT_KB2 = 64;          // filters per CTA of the staged kernels
+constexpr int OT_PITCH = OT_KB2 + 1;
+
+// NCHW destination: 8 adjacent tiles x 64 filters are staged, then written as 16-byte vectors along w (consecutive
+// lanes cover consecutive vectors of one output row, so a row segment of 8 tiles goes out as one contiguous run).
 template <int A, bool POOL, bool ZF, typename TP, typename TOut>
-__global__ void __launch_bounds__(256) output_transform_strip(OTArgs a) {
+__global__ void __launch_bounds__(256, 2) output_transform_strip(const OTArgs a) {
     constexpr int MO = POOL ? (A - 2) / 2 : (A - 2);
     constexpr int COLS = MO * OT_TX;
-    constexpr int PITCH = OT_KB + 1;
-    __shared__ float stage[MO * COLS * PITCH];
+    constexpr int VE = 16 / (int)sizeof(TOut);
+    constexpr int NVEC = COLS / VE;
+    static_assert(COLS % VE == 0 || COLS < VE, "row segment must split into whole vectors");
+    __shared__ float stage[MO * COLS * OT_PITCH];
 
-    const int kchunks = (a.K + OT_KB - 1) / OT_KB;
-    const int k0 = (blockIdx.x % kchunks) * OT_KB;
+    const int kchunks = (a.K + OT_KB2 - 1) / OT_KB2;
+    const int k0 = (blockIdx.x % kchunks) * OT_KB2;
     const int bx0 = (blockIdx.x / kchunks) * OT_TX;
     const int by = blockIdx.y;
     const int n = a.n0 + blockIdx.z;
-
     {
-        const int k_l = threadIdx.x % OT_KB, tl = threadIdx.x / OT_KB;
-        const int bx = bx0 + tl, k = k0 + k_l;
+        const int lane = threadIdx.x % 32, tl = threadIdx.x / 32;
+        const int bx = bx0 + tl, k = k0 + 2 * lane;
         if (bx < a.bnx && k < a.K) {
-            float res[MO][MO];
             const long long t = ((long long)blockIdx.z * a.bny + by) * a.bnx + bx;
-            tile_outputs<A, POOL, ZF, TP>(a, t, k, res);
-#pragma unroll
-            for (int p = 0; p < MO; ++p)
-#pragma unroll
-                for (int q = 0; q < MO; ++q) stage[(p * COLS + tl * MO + q) * PITCH + k_l] = res[p][q];
+            stage_pair<A, POOL, ZF, TP>(a, t, k, 2 * lane, stage, OT_PITCH, [&](int p, int q) { return p * COLS + tl * MO + q; });
         }
     }
     __syncthreads();
     TOut* __restrict__ y = (TOut*)a.y + (long long)n * a.sy.n;
-    for (int idx = threadIdx.x; idx < MO * COLS * OT_KB; idx += 256) {
-        const int col = idx % COLS;
-        const int rk = idx / COLS;
-        const int k_l = rk % OT_KB;
-        const int p = rk / OT_KB;
-        const int oy = by * MO + p, ox = bx0 * MO + col, k = k0 + k_l;
-        if (oy < a.ph && ox < a.pw && k < a.K)
-            y[(long long)k * a.sy.c + oy * a.sy.h + ox * a.sy.w] = from_float<TOut>(stage[(p * COLS + col) * PITCH + k_l]);
+    const int ox0 = bx0 * MO;
+    const bool vec_ok = NVEC > 0 && (a.pw % VE) == 0 && ((a.sy.n | a.sy.c) % VE) == 0 && (reinterpret_cast<uintptr_t>(a.y) & 15) == 0;
+    if (vec_ok) {
+        for (int idx = threadIdx.x; idx < MO * OT_KB2 * NVEC; idx += 256) {
+            const int vec = idx % NVEC;
+            const int rk = idx / NVEC;
+            const int k_l = rk % OT_KB2, p = rk / OT_KB2;
+            const int oy = by * MO + p, ox = ox0 + vec * VE, k = k0 + k_l;
+            if (oy >= a.ph || k >= a.K || ox >= a.pw) continue;
+            float v[VE];
+#pragma unroll
+            for (int e = 0; e < VE; ++e) v[e] = stage[(p * COLS + vec * VE + e) * OT_PITCH + k_l];
+            TOut* dst = y + (long long)k * a.sy.c + oy * a.sy.h + ox;
+            if (ox + VE <= a.pw) {
+                *reinterpret_cast<uint4*>(dst) = pack16<TOut>(v);
+            } else {
+                for (int e = 0; e < VE && ox + e < a.pw; ++e) dst[e] = from_float<TOut>(v[e]);
+            }
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < MO * COLS * OT_KB2; idx += 256) {
+            const int col = idx % COLS;
+            const int rk = idx / COLS;
+            const int k_l = rk % OT_KB2, p = rk / OT_KB2;
+            const int oy = by * MO + p, ox = ox0 + col, k = k0 + k_l;
+            if (oy < a.ph && ox < a.pw && k < a.K)
+                y[(long long)k * a.sy.c + oy * a.sy.h + ox * a.sy.w] = from_float<TOut>(stage[(p * COLS + col) * OT_PITCH + k_l]);
+        }
     }
 }
 
-// CHWN destination: stage 8 images x 32 filters of one tile position, store contiguous along n
+// CHWN destination: one tile position x 8 images x 64 filters are staged, then written as 16-byte vectors along n
 template <int A, bool POOL, bool ZF, typename TP, typename TOut>
-__global__ void __launch_bounds__(256) output_transform_batch(OTArgs a) {
+__global__ void __launch_bounds__(256, 2) output_transform_batch(const OTArgs a) {
     constexpr int MO = POOL ? (A - 2) / 2 : (A - 2);
-    constexpr int PITCH = OT_KB + 4;
-    __shared__ float stage[MO * MO * OT_NB * PITCH];
+    constexpr int VE = 16 / (int)sizeof(TOut);       // images per vector: 8 (bf16) or 4 (float)
+    constexpr int NVEC = OT_NB / VE;
+    __shared__ float stage[MO * MO * OT_NB * OT_PITCH];
 
-    const int kchunks = (a.K + OT_KB - 1) / OT_KB;
-    const int k0 = (blockIdx.x % kchunks) * OT_KB;
+    const int kchunks = (a.K + OT_KB2 - 1) / OT_KB2;
+    const int k0 = (blockIdx.x % kchunks) * OT_KB2;
     const int nb0 = (blockIdx.x / kchunks) * OT_NB;
     const int bx = blockIdx.y, by = blockIdx.z;
-
     {
-        const int k_l = threadIdx.x % OT_KB, n_l = threadIdx.x / OT_KB;
-        const int k = k0 + k_l;
+        const int lane = threadIdx.x % 32, n_l = threadIdx.x / 32;
+        const int k = k0 + 2 * lane;
         if (nb0 + n_l < a.ns && k < a.K) {
-            float res[MO][MO];
             const long long t = ((long long)(nb0 + n_l) * a.bny + by) * a.bnx + bx;
-            tile_outputs<A, POOL, ZF, TP>(a, t, k, res);
-#pragma unroll
-            for (int p = 0; p < MO; ++p)
-#pragma unroll
-                for (int q = 0; q < MO; ++q) stage[((p * MO + q) * OT_NB + n_l) * PITCH + k_l] = res[p][q];
+            stage_pair<A, POOL, ZF, TP>(a, t, k, 2 * lane, stage, OT_PITCH, [&](int p, int q) { return (p * MO + q) * OT_NB + n_l; });
         }
     }
     __syncthreads();
     TOut* __restrict__ y = (TOut*)a.y;
-    for (int idx = threadIdx.x; idx < MO * MO * OT_NB * OT_KB; idx += 256) {
-        const int n_l = idx % OT_NB;
-        const int rk = idx / OT_NB;
-        const int k_l = rk % OT_KB;
-        const int pq = rk / OT_KB;
+    const int nbase = a.n0 + nb0;
+    const bool vec_ok = ((a.sy.c | a.sy.h | a.sy.w) % VE) == 0 && (nbase % VE) == 0 && (reinterpret_cast<uintptr_t>(a.y) & 15) == 0;
+    for (int idx = threadIdx.x; idx < MO * MO * OT_KB2 * NVEC; idx += 256) {
+        const int k_l = idx % OT_KB2;
+        const int rv = idx / OT_KB2;
+        const int vec = rv % NVEC, pq = rv / NVEC;
         const int oy = by * MO + pq / MO, ox = bx * MO + pq % MO, k = k0 + k_l;
-        if (oy < a.ph && ox < a.pw && k < a.K && nb0 + n_l < a.ns)
-            y[(long long)(a.n0 + nb0 + n_l) * a.sy.n + (long long)k * a.sy.c + oy * a.sy.h + ox * a.sy.w] =
-                from_float<TOut>(stage[(pq * OT_NB + n_l) * PITCH + k_l]);
+        const int n_l0 = vec * VE;
+        if (oy >= a.ph || ox >= a.pw || k >= a.K || nb0 + n_l0 >= a.ns) continue;
+        float v[VE];
+#pragma unroll
+        for (int e = 0; e < VE; ++e) v[e] = stage[(pq * OT_NB + n_l0 + e) * OT_PITCH + k_l];
+        TOut* dst = y + (long long)k * a.sy.c + oy * a.sy.h + ox * a.sy.w + (nbase + n_l0);
+        if (vec_ok && nb0 + n_l0 + VE <= a.ns) {
+            *reinterpret_cast<uint4*>(dst) = pack16<TOut>(v);
+        } else {
+            for (int e = 0; e < VE && nb0 + n_l0 + e < a.ns; ++e) dst[e] = from_float<TOut>(v[e]);
+        }
     }
 }
 
 template <int A, bool POOL, bool ZF, typename TP, typename TOut>
 static int run(const wino_conv_desc& d, const Geometry& g, const OTArgs& a, cudaStream_t st) {
-    static_assert(OT_TX * OT_KB == 256 && OT_NB * OT_KB == 256, "one work item per thread");
-    const int kchunks = (d.k + OT_KB - 1) / OT_KB;
+    const int kchunks = (d.k + OT_KB - 1) / OT_KB, kchunks2 = (d.k + OT_KB2 - 1) / OT_KB2;
     ProfScope prof(STAGE_OUTPUT, st);
     count_launch();
     if (d.layout_out == WINO_NHWC && d.k % 2 == 0 && ((uintptr_t)a.m & 7) == 0 && ((uintptr_t)a.y & 7) == 0) {
@@ -280,10 +355,10 @@ static int run(const wino_conv_desc& d, const Geometry& g, const OTArgs& a, cuda
         const long long items = T * kchunks * OT_KB;
         output_transform_direct<A, POOL, ZF, TP, TOut><<<(unsigned)((items + 255) / 256), 256, 0, st>>>(a, T);
     } else if (d.layout_out == WINO_NCHW) {
-        dim3 grid((unsigned)(((g.bnx + OT_TX - 1) / OT_TX) * kchunks), (unsigned)g.bny, (unsigned)a.ns);
+        dim3 grid((unsigned)(((g.bnx + OT_TX - 1) / OT_TX) * kchunks2), (unsigned)g.bny, (unsigned)a.ns);
         output_transform_strip<A, POOL, ZF, TP, TOut><<<grid, 256, 0, st>>>(a);
     } else {
-        dim3 grid((unsigned)(((a.ns + OT_NB - 1) / OT_NB) * kchunks), (unsigned)g.bnx, (unsigned)g.bny);
+        dim3 grid((unsigned)(((a.ns + OT_NB - 1) / OT_NB) * kchunks2), (unsigned)g.bnx, (unsigned)g.bny);
         output_transform_batch<A, POOL, ZF, TP, TOut><<<grid, 256, 0, st>>>(a);
     }
     WINO_CUDA_CHECK(cudaGetLastError());
