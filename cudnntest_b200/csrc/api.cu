@@ -243,7 +243,10 @@ size_t wino_filter_bytes(const wino_conv_desc* d) {
     if (make_geometry(d, &g) != WINO_OK) return 0;
     const size_t wino = (size_t)g.a * g.a * d->k * g.cp * g.esize_op;
     // thin-input layers keep packed raw filters instead (always smaller); report the larger so either path fits
-    return direct_small_c_applies(*d) && direct_small_c_filter_bytes(*d) > wino ? direct_small_c_filter_bytes(*d) : wino;
+    size_t need = wino;
+    if (direct_small_c_applies(*d) && direct_small_c_filter_bytes(*d) > need) need = direct_small_c_filter_bytes(*d);
+    if (direct_tc_applies(*d) && direct_tc_filter_bytes(*d) > need) need = direct_tc_filter_bytes(*d);
+    return need;
 }
 
 size_t wino_conv_workspace_bytes(const wino_conv_desc* d) {
@@ -278,6 +281,7 @@ int wino_filter_transform(const wino_conv_desc* d, const void* w, void* u, wino_
     if (!w || !u) return fail(WINO_E_BADARG, "filter transform: NULL pointer");
     if ((rc = check_device())) return rc;
     if (direct_small_c_applies(*d)) return launch_direct_small_c_pack(*d, w, u, (cudaStream_t)stream);
+    if (direct_tc_applies(*d)) return launch_direct_tc_pack(*d, w, u, (cudaStream_t)stream);
     return launch_filter_transform(*d, g, w, u, (cudaStream_t)stream);
 }
 
@@ -347,6 +351,7 @@ int wino_conv_forward(const wino_conv_desc* d, const void* x, const void* u, con
     if (d->has_bias && !bias) return fail(WINO_E_BADARG, "conv forward: has_bias set but bias is NULL");
     if ((rc = check_device())) return rc;
     if (direct_small_c_applies(*d)) return launch_direct_small_c(*d, g, x, u, bias, y, (cudaStream_t)stream);
+    if (direct_tc_applies(*d)) return launch_direct_tc(*d, g, x, u, bias, y, (cudaStream_t)stream);
     const int ns = slab_images(*d, g);
     const long long tp = tile_rows(g, ns);
     const size_t need = v_bytes(g, tp) + prod_bytes(g, tp) + 1024;

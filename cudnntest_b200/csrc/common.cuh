@@ -138,6 +138,12 @@ int launch_output_transform(const wino_conv_desc& d, const Geometry& g, const vo
                             void* y, int n0, int ns, long long tp, cudaStream_t st);
 int launch_gemm_ffma(const float* v, const float* u, float* m, int batches, long long t_rows, long long tp, int k,
                      int cp, int kq, cudaStream_t st);
+// direct convolution on tensor cores for thin, large-spatial NHWC BF16 layers, C = 64 / 128 (direct_tc.cu)
+bool direct_tc_applies(const wino_conv_desc& d);
+size_t direct_tc_filter_bytes(const wino_conv_desc& d);
+int launch_direct_tc_pack(const wino_conv_desc& d, const void* w, void* packed, cudaStream_t st);
+int launch_direct_tc(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,
+                     cudaStream_t st);
 // thin-input (C <= 3) direct convolution on tensor cores (direct_small_c.cu)
 bool direct_small_c_applies(const wino_conv_desc& d);
 size_t direct_small_c_filter_bytes(const wino_conv_desc& d);

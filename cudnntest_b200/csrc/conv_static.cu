@@ -67,6 +67,7 @@ int wino_conv_forward_static(const wino_conv_desc* d, const void* x, const void*
     if (d->has_bias && !bias) return fail(WINO_E_BADARG, "conv forward (static scratch): has_bias set but bias is NULL");
     if ((rc = check_device())) return rc;
     if (direct_small_c_applies(*d)) return launch_direct_small_c(*d, g, x, u, bias, y, (cudaStream_t)stream);   // needs no scratch
+    if (direct_tc_applies(*d)) return launch_direct_tc(*d, g, x, u, bias, y, (cudaStream_t)stream);               // needs no scratch
 
     // largest slab whose V + M (with the same 1 KiB carving as wino_conv_forward) fits the array
     const size_t one = v_bytes(g, tile_rows(g, 1)) + prod_bytes(g, tile_rows(g, 1)) + 1024;

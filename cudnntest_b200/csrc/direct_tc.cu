@@ -1,0 +1,357 @@
+// Direct (implicit-GEMM) 3x3 convolution on tcgen05 for thin, large-spatial NHWC BF16 layers (C = 64, 128), sm_100a.
+//
+// Why it exists: for C <= 128 the Winograd pipeline is bound by writing and re-reading its transform-domain
+// buffers (V and the products are 2.25x / 1.5x the size of the activations), while the direct convolution of such
+// a layer only has to read x and write y once and its 9x larger tensor work is still far below the tensor roof.
+// The reference has a direct convolution of the same shape of idea on CUDA cores that it never launches
+// (Conv_fuse, fusedTest/winotrans.cuh:1868-1992); its live path sends every layer through Winograd.
+//
+//   * output tile = 8 (w) x 16 (h) pixels of one image = the 128 rows of the MMA; filters in blocks of BN;
+//   * per 64-channel chunk ONE 4-D cp.async.bulk.tensor load brings the 16 (w) x 18 (h) x 128-byte halo box of the
+//     tile into a 128-byte-swizzled ring slot (zero padding = the TMA unit's out-of-range fill).  The operand of
+//     filter tap (r, s) is that same slot read through a shared-memory matrix descriptor that starts at pixel
+//     (r, s) of the box: 8-pixel row groups 2048 bytes apart, start address advanced by (16 r + s) * 128 bytes
+//     (the swizzle phase follows the address).  Nine taps x four K-steps of tcgen05.mma per chunk reuse one load;
+//   * filter tiles Wd[tap][K][Cp] are either resident in shared memory for the whole kernel (9 * chunks * BN rows
+//     <= 80 KB) or streamed through their own ring;
+//   * epilogue warps read their accumulator lane (= pixel) from tensor memory, add bias, apply ReLU and, for
+//     block-ending layers, take the 2x2 max with two warp shuffles (the tile's pixel order puts the 2x2 window in
+//     lanes l, l^1, l^8, l^9), then store 16-byte vectors of the pixel's BN contiguous NHWC channels.
+// Bound: tensor pipe (2*N*K*C*OH*OW*9 flops) once the loads are hidden; HBM traffic is x + y only.
+#include <cstdlib>
+#include <mutex>
+
+#include "common.cuh"
+#include "ptx.cuh"
+#include "tcgen05.cuh"
+
+namespace wino {
+
+namespace {
+
+constexpr int DT_TW = 8, DT_TH = 16;                 // output tile
+constexpr int DT_BOX_W = 16, DT_BOX_H = DT_TH + 2;   // halo box (w padded to 16 so row groups stay 1 KiB-phase aligned)
+constexpr int DT_A_BYTES = DT_BOX_W * DT_BOX_H * 128;
+constexpr int DT_THREADS = 192;
+
+enum DtWaitCode { DT_W_A_EMPTY = 41, DT_W_A_FULL = 42, DT_W_B_EMPTY = 43, DT_W_B_FULL = 44, DT_W_T_EMPTY = 45, DT_W_T_FULL = 46,
+                  DT_W_B_RESIDENT = 47 };
+
+struct DtParams {
+    const float* bias;
+    __nv_bfloat16* y;
+    int N, OH, OW, K, pad;
+    int PH, PW;                  // stored output size (after the optional pool)
+    int tiles_x, tiles_y, nblocks, cchunks;
+    int relu, pool;
+    uint32_t idesc;
+    int* status;
+};
+
+// K-major, 128-byte swizzle, 8-row groups `sbo` bytes apart.  The start address may be any 128-byte row of a
+// swizzled box: the MMA unit derives the swizzle phase of every row from its shared-memory address (measured: the
+// descriptor's base-offset field must stay 0 for starts that are not 1 KiB aligned, the results are wrong with
+// base offset = row phase).
+__device__ __forceinline__ uint64_t smem_desc_k128_sbo(uint32_t saddr, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(sbo >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+template <int BN, int A_STAGES, int B_STAGES, bool B_RESIDENT>
+struct DtSmem {
+    static constexpr int B_TILE = BN * 128;
+    static constexpr int A_OFF = 0;
+    static constexpr int B_OFF = A_OFF + A_STAGES * DT_A_BYTES;
+    static constexpr int B_BYTES = (B_RESIDENT ? 10 : B_STAGES) * B_TILE;      // resident: the 9 taps of one chunk (<= 80 KB)
+    static constexpr int BAR_OFF = B_OFF + B_BYTES;
+    static constexpr int NBARS = 2 * A_STAGES + 2 * B_STAGES + 4 + 1;
+    static constexpr int SLOT_OFF = BAR_OFF + 8 * NBARS;
+    static constexpr int TOTAL = SLOT_OFF + 16 + 1024;
+};
+
+template <int BN, int A_STAGES, int B_STAGES, bool B_RESIDENT>
+__global__ void __launch_bounds__(DT_THREADS, 1)
+direct_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const DtParams p) {
+    using L = DtSmem<BN, A_STAGES, B_STAGES, B_RESIDENT>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + L::BAR_OFF;
+    const uint32_t bar_afull = bars, bar_aempty = bar_afull + 8 * A_STAGES;
+    const uint32_t bar_bfull = bar_aempty + 8 * A_STAGES, bar_bempty = bar_bfull + 8 * B_STAGES;
+    const uint32_t bar_tfull = bar_bempty + 8 * B_STAGES, bar_tempty = bar_tfull + 16, bar_bres = bar_tempty + 16;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::SLOT_OFF);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::SLOT_OFF + 4);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < A_STAGES; ++s) { mbar_init(bar_afull + 8 * s, 1); mbar_init(bar_aempty + 8 * s, 1); }
+        for (int s = 0; s < B_STAGES; ++s) { mbar_init(bar_bfull + 8 * s, 1); mbar_init(bar_bempty + 8 * s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 128); }
+        mbar_init(bar_bres, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), 2 * BN < 32 ? 32 : 2 * BN);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const long long tiles_img = (long long)p.tiles_x * p.tiles_y;
+    const long long total = (long long)p.N * tiles_img * p.nblocks;
+    // with resident filters a CTA keeps one filter block: it only walks tiles of its own nb
+    const int my_nb = B_RESIDENT ? (int)(blockIdx.x % p.nblocks) : 0;
+
+    auto decode = [&](long long t, int& n, int& ty, int& tx, int& nb) {
+        nb = (int)(t % p.nblocks); t /= p.nblocks;
+        tx = (int)(t % p.tiles_x); t /= p.tiles_x;
+        ty = (int)(t % p.tiles_y);
+        n = (int)(t / p.tiles_y);
+    };
+    const long long first = B_RESIDENT ? (long long)(blockIdx.x / p.nblocks) * p.nblocks + my_nb : blockIdx.x;
+    const long long step = B_RESIDENT ? (long long)(gridDim.x / p.nblocks) * p.nblocks : gridDim.x;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            if (B_RESIDENT) {       // all taps and chunks of this CTA's filter block, once
+                mbar_arrive_expect_tx(bar_bres, (uint32_t)(9 * p.cchunks * L::B_TILE));
+                for (int ch = 0; ch < p.cchunks; ++ch)
+                    for (int tap = 0; tap < 9; ++tap)
+                        tma_load_3d(base + L::B_OFF + (ch * 9 + tap) * L::B_TILE, &tm_w, bar_bres, ch * 64, my_nb * BN, tap);
+            }
+            unsigned long long acount = 0, bcount = 0;
+            for (long long t = first; ok && t < total; t += step) {
+                int n, ty, tx, nb;
+                decode(t, n, ty, tx, nb);
+                for (int ch = 0; ok && ch < p.cchunks; ++ch) {
+                    const int st = (int)(acount % A_STAGES);
+                    if (!mbar_wait_bounded(bar_aempty + 8 * st, (uint32_t)(((acount / A_STAGES) & 1) ^ 1), abort_flag, p.status, DT_W_A_EMPTY)) { ok = false; break; }
+                    mbar_arrive_expect_tx(bar_afull + 8 * st, DT_A_BYTES);
+                    tma_load_4d(base + L::A_OFF + st * DT_A_BYTES, &tm_x, bar_afull + 8 * st, ch * 64, tx * DT_TW - p.pad, ty * DT_TH - p.pad, n);
+                    ++acount;
+                    if (!B_RESIDENT) {
+                        for (int tap = 0; tap < 9; ++tap) {
+                            const int sb = (int)(bcount % B_STAGES);
+                            if (!mbar_wait_bounded(bar_bempty + 8 * sb, (uint32_t)(((bcount / B_STAGES) & 1) ^ 1), abort_flag, p.status, DT_W_B_EMPTY)) { ok = false; break; }
+                            mbar_arrive_expect_tx(bar_bfull + 8 * sb, L::B_TILE);
+                            tma_load_3d(base + L::B_OFF + sb * L::B_TILE, &tm_w, bar_bfull + 8 * sb, ch * 64, nb * BN, tap);
+                            ++bcount;
+                        }
+                    }
+                }
+            }
+            if (!ok) drain_after_abort();
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = true;
+            if (B_RESIDENT) ok = mbar_wait_bounded(bar_bres, 0, abort_flag, p.status, DT_W_B_RESIDENT);
+            unsigned long long acount = 0, bcount = 0;
+            int as = 0;
+            uint32_t aphase = 0;
+            for (long long t = first; ok && t < total; t += step) {
+                if (!mbar_wait_bounded(bar_tempty + 8 * as, aphase ^ 1, abort_flag, p.status, DT_W_T_EMPTY)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(as * BN);
+                for (int ch = 0; ok && ch < p.cchunks; ++ch) {
+                    const int st = (int)(acount % A_STAGES);
+                    if (!mbar_wait_bounded(bar_afull + 8 * st, (uint32_t)((acount / A_STAGES) & 1), abort_flag, p.status, DT_W_A_FULL)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_s = base + L::A_OFF + st * DT_A_BYTES;
+                    for (int tap = 0; tap < 9; ++tap) {
+                        uint32_t b_s;
+                        int sb = 0;
+                        if (B_RESIDENT) {
+                            b_s = base + L::B_OFF + (ch * 9 + tap) * L::B_TILE;
+                        } else {
+                            sb = (int)(bcount % B_STAGES);
+                            if (!mbar_wait_bounded(bar_bfull + 8 * sb, (uint32_t)((bcount / B_STAGES) & 1), abort_flag, p.status, DT_W_B_FULL)) { ok = false; break; }
+                            tc_fence_after();
+                            b_s = base + L::B_OFF + sb * L::B_TILE;
+                        }
+                        const int r = tap / 3, s = tap % 3;
+                        const uint32_t a_tap = a_s + (uint32_t)((r * DT_BOX_W + s) * 128);
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks)
+                            tc_mma<false>(d_tmem, smem_desc_k128_sbo(a_tap + ks * 32, DT_BOX_W * 128), smem_desc_k128(b_s + ks * 32), p.idesc,
+                                          (ch | tap | ks) ? 1u : 0u);
+                        if (!B_RESIDENT) { tc_commit(bar_bempty + 8 * sb); ++bcount; }
+                    }
+                    if (!ok) break;
+                    tc_commit(bar_aempty + 8 * st);
+                    ++acount;
+                }
+                if (ok) tc_commit(bar_tfull + 8 * as);
+                as ^= 1;
+                if (as == 0) aphase ^= 1;
+            }
+        }
+    } else {
+        const int quarter = warp % 4;
+        const int l = quarter * 32 + lane;            // accumulator lane = pixel of the tile: h = l / 8, w = l % 8
+        const int ph_ = l / DT_TW, pw_ = l % DT_TW;
+        int as = 0;
+        uint32_t aphase = 0;
+        bool ok = true;
+        for (long long t = first; ok && t < total; t += step) {
+            int n, ty, tx, nb;
+            decode(t, n, ty, tx, nb);
+            if (!mbar_wait_bounded(bar_tfull + 8 * as, aphase, abort_flag, p.status, DT_W_T_FULL)) ok = false;
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int oy = ty * DT_TH + ph_, ox = tx * DT_TW + pw_;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * BN);
+#pragma unroll 1
+            for (int chunk = 0; chunk < BN / 32; ++chunk) {
+                uint32_t r[32];
+                tmem_ld_32x32(lane_addr + chunk * 32, r);
+                tmem_ld_wait();
+                if (chunk == BN / 32 - 1) {
+                    tc_fence_before();
+                    mbar_arrive(bar_tempty + 8 * as);
+                }
+                const int k0 = nb * BN + chunk * 32;
+                float v[32];
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    float val = __uint_as_float(r[e]) + ((p.bias && k0 + e < p.K) ? __ldg(p.bias + k0 + e) : 0.f);
+                    v[e] = p.relu ? fmaxf(val, 0.f) : val;
+                }
+                bool writer;
+                long long pix;
+                if (p.pool) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        float m = fmaxf(v[e], __shfl_xor_sync(0xffffffffu, v[e], 1));
+                        v[e] = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+                    }
+                    writer = ((ph_ | pw_) & 1) == 0 && (oy >> 1) < p.PH && (ox >> 1) < p.PW;
+                    pix = ((long long)n * p.PH + (oy >> 1)) * p.PW + (ox >> 1);
+                } else {
+                    writer = oy < p.OH && ox < p.OW;
+                    pix = ((long long)n * p.OH + oy) * p.OW + ox;
+                }
+                if (writer) {
+                    __nv_bfloat16* dst = p.y + pix * p.K + k0;
+                    if (k0 + 32 <= p.K && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t w4[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * c + 2 * e], v[8 * c + 2 * e + 1]);
+                                w4[e] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                            reinterpret_cast<uint4*>(dst)[c] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                        }
+                    } else {
+                        for (int e = 0; e < 32 && k0 + e < p.K; ++e) dst[e] = __float2bfloat16_rn(v[e]);
+                    }
+                }
+            }
+            as ^= 1;
+            if (as == 0) aphase ^= 1;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 2 * BN < 32 ? 32 : 2 * BN);
+    }
+}
+
+// Filters for the kernel above: Wd[tap = 3r + s][k][Cp] = w[k][c][r][s] (any filter layout in, bf16), zero beyond C
+__global__ void pack_direct_tc_filters(const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, int K, int C, int Cp,
+                                       Strides sw) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)9 * K * Cp) return;
+    const int c = (int)(idx % Cp);
+    const int k = (int)((idx / Cp) % K);
+    const int tap = (int)(idx / ((long long)Cp * K));
+    out[idx] = c < C ? w[k * sw.n + c * sw.c + (tap / 3) * sw.h + (tap % 3) * sw.w] : __float2bfloat16(0.f);
+}
+
+template <int BN, int A_STAGES, int B_STAGES, bool B_RESIDENT>
+int run(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const DtParams& p, cudaStream_t st) {
+    using L = DtSmem<BN, A_STAGES, B_STAGES, B_RESIDENT>;
+    static_assert(L::TOTAL <= 232448, "shared memory budget of one CTA exceeded");
+    static std::once_flag once[64];
+    int dev = 0;
+    WINO_CUDA_CHECK(cudaGetDevice(&dev));
+    cudaError_t attr_err = cudaSuccess;
+    std::call_once(once[dev & 63], [&] {
+        attr_err = cudaFuncSetAttribute(direct_tc_kernel<BN, A_STAGES, B_STAGES, B_RESIDENT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    });
+    WINO_CUDA_CHECK(attr_err);
+    const long long total = (long long)p.N * p.tiles_x * p.tiles_y * p.nblocks;
+    long long grid = total < sm_count() ? total : sm_count();
+    if (B_RESIDENT) grid = grid / p.nblocks * p.nblocks;      // every CTA owns one filter block
+    if (grid < 1) grid = p.nblocks;
+    ProfScope prof(STAGE_DIRECT, st);
+    count_launch();
+    direct_tc_kernel<BN, A_STAGES, B_STAGES, B_RESIDENT><<<(unsigned)grid, DT_THREADS, L::TOTAL, st>>>(tm_x, tm_w, p);
+    WINO_CUDA_CHECK(cudaGetLastError());
+    return WINO_OK;
+}
+
+}  // namespace
+
+bool direct_tc_applies(const wino_conv_desc& d) {
+    static const int mode = [] { const char* e = getenv("WINO_DIRECT_TC"); return e ? atoi(e) : 1; }();
+    if (mode == 0) return false;
+    return d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC && d.dtype == WINO_BF16 && d.c % 64 == 0 && d.c <= 128 &&
+           d.k % 8 == 0 && (d.wino == 0);
+}
+
+size_t direct_tc_filter_bytes(const wino_conv_desc& d) { return (size_t)9 * d.k * d.c * 2; }
+
+int launch_direct_tc_pack(const wino_conv_desc& d, const void* w, void* packed, cudaStream_t st) {
+    const long long total = (long long)9 * d.k * d.c;
+    ProfScope prof(STAGE_FILTER, st);
+    count_launch();
+    pack_direct_tc_filters<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)packed, d.k, d.c, d.c,
+                                                                          filter_strides(d.layout_in, d.k, d.c));
+    WINO_CUDA_CHECK(cudaGetLastError());
+    return WINO_OK;
+}
+
+int launch_direct_tc(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,
+                     cudaStream_t st) {
+    if (d.n == 0) return WINO_OK;
+    if (((uintptr_t)x | (uintptr_t)packed | (uintptr_t)y) & 15) return fail(WINO_E_BADARG, "direct conv: buffers must be 16-byte aligned");
+    DtParams p;
+    p.bias = d.has_bias ? bias : nullptr; p.y = (__nv_bfloat16*)y;
+    p.N = d.n; p.OH = g.oh; p.OW = g.ow; p.K = d.k; p.pad = d.pad; p.PH = g.ph; p.PW = g.pw;
+    p.tiles_x = (g.ow + DT_TW - 1) / DT_TW; p.tiles_y = (g.oh + DT_TH - 1) / DT_TH;
+    p.cchunks = d.c / 64;
+    p.relu = d.relu; p.pool = d.pool2x2;
+    int rc = status_word(&p.status);
+    if (rc) return rc;
+    const int bn = d.k >= 128 ? 128 : 64;
+    p.nblocks = (d.k + bn - 1) / bn;
+    p.idesc = make_idesc(OP_BF16, bn);
+    CUtensorMap tm_x, tm_w;
+    {
+        const unsigned long long dims[4] = {(unsigned long long)d.c, (unsigned long long)d.w, (unsigned long long)d.h, (unsigned long long)d.n};
+        const unsigned long long strides[3] = {d.c * 2ull, (unsigned long long)d.w * d.c * 2ull, (unsigned long long)d.h * d.w * d.c * 2ull};
+        const unsigned box[4] = {64u, (unsigned)DT_BOX_W, (unsigned)DT_BOX_H, 1u};
+        if ((rc = encode_tensor_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, x, dims, strides, box, true))) return rc;
+    }
+    if ((rc = make_map_k128(&tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, packed, d.c, d.k, d.k, 9, bn))) return rc;
+    const bool resident = 9 * p.cchunks * bn * 128 <= 80 * 1024;
+    if (bn == 64) return resident ? run<64, 3, 2, true>(tm_x, tm_w, p, st) : run<64, 3, 6, false>(tm_x, tm_w, p, st);
+    return run<128, 3, 4, false>(tm_x, tm_w, p, st);
+}
+
+}  // namespace wino
