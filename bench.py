@@ -273,8 +273,9 @@ def run_ours(args, rank, world, local_rank):
     # Roofline of the kernel class with the largest share of the step.  Algorithmic bytes / flops per launch set
     # come from vgg.kernel_model (every layer's units summed per kernel class); the bound is whichever of
     # bytes / HBM peak and flops / tensor peak is the longer time.
-    model = vgg.kernel_model(args.batch, args.dtype, args.wino or 4)
-    classes = {"input_transform": 0, "tile_gemm_plain": 1, "output_transform": 2, "tile_gemm_rowfused": 4, "direct_thin_input": 5}
+    model = vgg.kernel_model(args.batch, args.dtype, args.wino or 4, layout=args.layout, forced_wino=bool(args.wino))
+    classes = {"input_transform": 0, "tile_gemm_plain": 1, "output_transform": 2, "tile_gemm_rowfused": 4, "direct_thin_input": 5,
+               "direct_tensor_core": 6}
     stage = {n: {"ms": float(stage_ms[i]), "launches": int(stage_n[i])} for n, i in classes.items()}
     dominant = max(classes, key=lambda n: stage[n]["ms"])
     tpeak = peaks["tflops_sustained"] * (0.5 if args.dtype == "tf32" else 1.0)
@@ -283,7 +284,7 @@ def run_ours(args, rank, world, local_rank):
     t_hbm, t_tc = byts / (peaks["hbm_gbs"] * 1e9), flops / (tpeak * 1e12)
     kernel_names = {"input_transform": "input_transform_nhwc_tma", "tile_gemm_plain": "gemm_tc_kernel" if args.dtype != "fp32" else "gemm_ffma_kernel",
                     "output_transform": "output_transform_direct", "tile_gemm_rowfused": "gemm_tc_z_kernel",
-                    "direct_thin_input": "direct_small_c_kernel"}
+                    "direct_thin_input": "direct_small_c_kernel", "direct_tensor_core": "direct_tc_kernel"}
     if t_hbm >= t_tc or args.dtype == "fp32":
         achieved = byts / t_meas / 1e9
         roofline = {"kernel": kernel_names[dominant], "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",

@@ -120,7 +120,7 @@ int check_device();
 
 // ---- measurement hooks -----------------------------------------------------------------------------------
 void count_launch();
-enum Stage { STAGE_INPUT = 0, STAGE_GEMM = 1, STAGE_OUTPUT = 2, STAGE_FILTER = 3, STAGE_GEMM_ROWFUSED = 4, STAGE_DIRECT = 5, STAGE_COUNT = 8 };
+enum Stage { STAGE_INPUT = 0, STAGE_GEMM = 1, STAGE_OUTPUT = 2, STAGE_FILTER = 3, STAGE_GEMM_ROWFUSED = 4, STAGE_DIRECT = 5, STAGE_DIRECT_TC = 6, STAGE_COUNT = 8 };
 // brackets one kernel launch with CUDA events when profiling is enabled
 struct ProfScope {
     ProfScope(int stage, cudaStream_t st);

@@ -32,7 +32,8 @@ namespace {
 constexpr int DT_TW = 8, DT_TH = 16;                 // output tile
 constexpr int DT_BOX_W = 16, DT_BOX_H = DT_TH + 2;   // halo box (w padded to 16 so row groups stay 1 KiB-phase aligned)
 constexpr int DT_A_BYTES = DT_BOX_W * DT_BOX_H * 128;
-constexpr int DT_THREADS = 192;
+constexpr int DT_EPI_WARPS = 8;                      // two warps per tensor-memory lane quarter, each takes half the filter columns
+constexpr int DT_THREADS = 64 + 32 * DT_EPI_WARPS;
 
 enum DtWaitCode { DT_W_A_EMPTY = 41, DT_W_A_FULL = 42, DT_W_B_EMPTY = 43, DT_W_B_FULL = 44, DT_W_T_EMPTY = 45, DT_W_T_FULL = 46,
                   DT_W_B_RESIDENT = 47 };
@@ -92,7 +93,7 @@ direct_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     if (threadIdx.x == 0) {
         for (int s = 0; s < A_STAGES; ++s) { mbar_init(bar_afull + 8 * s, 1); mbar_init(bar_aempty + 8 * s, 1); }
         for (int s = 0; s < B_STAGES; ++s) { mbar_init(bar_bfull + 8 * s, 1); mbar_init(bar_bempty + 8 * s, 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 128); }
+        for (int a = 0; a < 2; ++a) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 32 * DT_EPI_WARPS); }
         mbar_init(bar_bres, 1);
         *abort_flag = 0;
         mbar_fence_init();
@@ -195,8 +196,10 @@ direct_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         }
     } else {
         const int quarter = warp % 4;
+        const int half = (warp - 2) / 4;              // which half of the BN filter columns this warp drains
         const int l = quarter * 32 + lane;            // accumulator lane = pixel of the tile: h = l / 8, w = l % 8
         const int ph_ = l / DT_TW, pw_ = l % DT_TW;
+        constexpr int CHUNKS = BN / 64;               // 32-column chunks per warp
         int as = 0;
         uint32_t aphase = 0;
         bool ok = true;
@@ -208,52 +211,59 @@ direct_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             if (!ok) break;
             tc_fence_after();
             const int oy = ty * DT_TH + ph_, ox = tx * DT_TW + pw_;
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * BN);
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * BN + half * (BN / 2));
+            bool writer;
+            long long pix;
+            if (p.pool) {
+                writer = ((ph_ | pw_) & 1) == 0 && (oy >> 1) < p.PH && (ox >> 1) < p.PW;
+                pix = ((long long)n * p.PH + (oy >> 1)) * p.PW + (ox >> 1);
+            } else {
+                writer = oy < p.OH && ox < p.OW;
+                pix = ((long long)n * p.OH + oy) * p.OW + ox;
+            }
 #pragma unroll 1
-            for (int chunk = 0; chunk < BN / 32; ++chunk) {
+            for (int chunk = 0; chunk < CHUNKS; ++chunk) {
                 uint32_t r[32];
                 tmem_ld_32x32(lane_addr + chunk * 32, r);
                 tmem_ld_wait();
-                if (chunk == BN / 32 - 1) {
+                if (chunk == CHUNKS - 1) {
                     tc_fence_before();
                     mbar_arrive(bar_tempty + 8 * as);
                 }
-                const int k0 = nb * BN + chunk * 32;
-                float v[32];
+                const int k0 = nb * BN + half * (BN / 2) + chunk * 32;
+                // bias + ReLU, packed to bf16 pairs; the 2x2 max is taken on the packed values (rounding is monotonic)
+                uint32_t w[16];
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    float val = __uint_as_float(r[e]) + ((p.bias && k0 + e < p.K) ? __ldg(p.bias + k0 + e) : 0.f);
-                    v[e] = p.relu ? fmaxf(val, 0.f) : val;
+                for (int e = 0; e < 32; e += 4) {
+                    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (p.bias && k0 + e + 4 <= p.K) b4 = __ldg(reinterpret_cast<const float4*>(p.bias + k0 + e));
+                    float v0 = __uint_as_float(r[e]) + b4.x, v1 = __uint_as_float(r[e + 1]) + b4.y;
+                    float v2 = __uint_as_float(r[e + 2]) + b4.z, v3 = __uint_as_float(r[e + 3]) + b4.w;
+                    if (p.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); v2 = fmaxf(v2, 0.f); v3 = fmaxf(v3, 0.f); }
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(v0, v1), h1 = __floats2bfloat162_rn(v2, v3);
+                    w[e / 2] = *reinterpret_cast<uint32_t*>(&h0);
+                    w[e / 2 + 1] = *reinterpret_cast<uint32_t*>(&h1);
                 }
-                bool writer;
-                long long pix;
                 if (p.pool) {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        float m = fmaxf(v[e], __shfl_xor_sync(0xffffffffu, v[e], 1));
-                        v[e] = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+                    for (int e = 0; e < 16; ++e) {
+                        uint32_t o = __shfl_xor_sync(0xffffffffu, w[e], 1);
+                        __nv_bfloat162 m = __hmax2(*reinterpret_cast<__nv_bfloat162*>(&w[e]), *reinterpret_cast<__nv_bfloat162*>(&o));
+                        uint32_t mu = *reinterpret_cast<uint32_t*>(&m);
+                        o = __shfl_xor_sync(0xffffffffu, mu, 8);
+                        m = __hmax2(m, *reinterpret_cast<__nv_bfloat162*>(&o));
+                        w[e] = *reinterpret_cast<uint32_t*>(&m);
                     }
-                    writer = ((ph_ | pw_) & 1) == 0 && (oy >> 1) < p.PH && (ox >> 1) < p.PW;
-                    pix = ((long long)n * p.PH + (oy >> 1)) * p.PW + (ox >> 1);
-                } else {
-                    writer = oy < p.OH && ox < p.OW;
-                    pix = ((long long)n * p.OH + oy) * p.OW + ox;
                 }
                 if (writer) {
                     __nv_bfloat16* dst = p.y + pix * p.K + k0;
                     if (k0 + 32 <= p.K && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            uint32_t w4[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * c + 2 * e], v[8 * c + 2 * e + 1]);
-                                w4[e] = *reinterpret_cast<uint32_t*>(&h);
-                            }
-                            reinterpret_cast<uint4*>(dst)[c] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
-                        }
+                        for (int c = 0; c < 4; ++c) reinterpret_cast<uint4*>(dst)[c] = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
                     } else {
-                        for (int e = 0; e < 32 && k0 + e < p.K; ++e) dst[e] = __float2bfloat16_rn(v[e]);
+#pragma unroll
+                        for (int e = 0; e < 32; ++e)
+                            if (k0 + e < p.K) dst[e] = reinterpret_cast<const __nv_bfloat16*>(w)[e];
                     }
                 }
             }
@@ -298,7 +308,7 @@ int run(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const DtParams& p, cud
     long long grid = total < sm_count() ? total : sm_count();
     if (B_RESIDENT) grid = grid / p.nblocks * p.nblocks;      // every CTA owns one filter block
     if (grid < 1) grid = p.nblocks;
-    ProfScope prof(STAGE_DIRECT, st);
+    ProfScope prof(STAGE_DIRECT_TC, st);
     count_launch();
     direct_tc_kernel<BN, A_STAGES, B_STAGES, B_RESIDENT><<<(unsigned)grid, DT_THREADS, L::TOTAL, st>>>(tm_x, tm_w, p);
     WINO_CUDA_CHECK(cudaGetLastError());
@@ -329,7 +339,8 @@ int launch_direct_tc_pack(const wino_conv_desc& d, const void* w, void* packed, 
 int launch_direct_tc(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,
                      cudaStream_t st) {
     if (d.n == 0) return WINO_OK;
-    if (((uintptr_t)x | (uintptr_t)packed | (uintptr_t)y) & 15) return fail(WINO_E_BADARG, "direct conv: buffers must be 16-byte aligned");
+    if (((uintptr_t)x | (uintptr_t)packed | (uintptr_t)y | (d.has_bias ? (uintptr_t)bias : 0)) & 15)
+        return fail(WINO_E_BADARG, "direct conv: buffers (and the bias) must be 16-byte aligned");
     DtParams p;
     p.bias = d.has_bias ? bias : nullptr; p.y = (__nv_bfloat16*)y;
     p.N = d.n; p.OH = g.oh; p.OW = g.ow; p.K = d.k; p.pad = d.pad; p.PH = g.ph; p.PW = g.pw;

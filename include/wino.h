@@ -136,7 +136,8 @@ int wino_maxpool2x2(int layout, int n, int c, int h, int w, int dtype, const voi
  * per-stage breakdown of comparison/wrapedConv_NCHW.cuh:88-138).  wino_profile_read synchronises the
  * device, adds up the elapsed milliseconds and launches per kernel class since the last read (index 0 input
  * transform, 1 plain tile GEMM (tensor-core or FFMA), 2 output transform, 3 filter transform, 4 row-fused
- * tile GEMM, 5 thin-input direct convolution, 6-7 unused) and clears the record. */
+ * tile GEMM, 5 thin-input (C <= 3) direct convolution, 6 direct tensor-core convolution (C = 64 / 128), 7 unused)
+ * and clears the record. */
 long long wino_launch_count(void);
 int wino_profile_enable(int on);
 int wino_profile_read(float stage_ms[8], long long stage_launches[8]);

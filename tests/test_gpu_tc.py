@@ -141,6 +141,32 @@ def test_thin_input_direct_path(cb, dtype, layout, shape):
     assert rel_l2(y3, oracle.conv_f64(x, wt, pad=0)) <= TOL_L2
 
 
+@pytest.mark.parametrize("shape,pool", [((2, 64, 32, 24, 64), False), ((2, 64, 32, 24, 64), True), ((1, 128, 20, 20, 128), False),
+                                        ((3, 64, 17, 13, 72), True), ((2, 128, 16, 16, 256), False), ((1, 64, 5, 37, 8), False),
+                                        ((2, 128, 40, 9, 200), True)])
+def test_direct_tensor_core_path(cb, shape, pool):
+    """NHWC BF16 layers with C = 64 / 128 and no explicit tile size run the implicit-GEMM kernel (halo box + shifted
+    descriptors): against the oracle, against the Winograd path, with and without the fused pool, ragged edges."""
+    n, c, h, w, k = shape
+    x, wt, b = make_inputs(n, c, h, w, k, seed=sum(shape) + 3)
+    ref = oracle.conv_f64(x, wt, bias=b, relu=True, pool=pool)
+    y = run_conv(x, wt, b, "NHWC", dtype="bf16", relu=True, pool=pool)              # wino = 0 -> engine's choice: direct
+    assert y.shape == ref.shape
+    assert rel_l2(y, ref) <= TOL_L2
+    yw = run_conv(x, wt, b, "NHWC", dtype="bf16", relu=True, pool=pool, wino=4)     # forced Winograd
+    assert rel_l2(yw, ref) <= TOL_L2
+    assert rel_l2(y, yw.astype(np.float64)) <= 2 * TOL_L2
+    y0 = run_conv(x, wt, None, "NHWC", dtype="bf16", pad=0)
+    assert rel_l2(y0, oracle.conv_f64(x, wt, pad=0)) <= TOL_L2
+
+
+def test_second_vgg_layer_full_size(cb):
+    """64 -> 64 at 224 x 224 with the fused pool, BF16 NHWC, 2 images: against the oracle."""
+    x, wt, b = make_inputs(2, 64, 224, 224, 64, seed=0xC0DE0042)
+    y = run_conv(x, wt, b, "NHWC", dtype="bf16", relu=True, pool=True)
+    assert rel_l2(y, oracle.conv_f64(x, wt, bias=b, relu=True, pool=True)) <= TOL_L2
+
+
 def test_first_vgg_layer_full_size(cb):
     """3 -> 64 at 224 x 224, BF16 NHWC, 4 images: against the oracle."""
     x, wt, b = make_inputs(4, 3, 224, 224, 64, seed=0xC0DE0041)
