@@ -30,8 +30,9 @@ namespace wino {
 namespace {
 
 constexpr int DT_TW = 8, DT_TH = 16;                 // output tile
-constexpr int DT_BOX_W = 16, DT_BOX_H = DT_TH + 2;   // halo box (w padded to 16 so row groups stay 1 KiB-phase aligned)
-constexpr int DT_A_BYTES = DT_BOX_W * DT_BOX_H * 128;
+constexpr int DT_BOX_W = DT_TW + 2, DT_BOX_H = DT_TH + 2;   // halo box: 10 x 18 pixels
+constexpr int DT_A_BYTES = DT_BOX_W * DT_BOX_H * 128;                      // bytes one halo box brings in
+constexpr int DT_A_STRIDE = (DT_A_BYTES + 1023) / 1024 * 1024;            // ring slots stay 1 KiB aligned
 constexpr int DT_EPI_WARPS = 8;                      // two warps per tensor-memory lane quarter, each takes half the filter columns
 constexpr int DT_THREADS = 64 + 32 * DT_EPI_WARPS;
 
@@ -67,7 +68,7 @@ template <int BN, int A_STAGES, int B_STAGES, bool B_RESIDENT>
 struct DtSmem {
     static constexpr int B_TILE = BN * 128;
     static constexpr int A_OFF = 0;
-    static constexpr int B_OFF = A_OFF + A_STAGES * DT_A_BYTES;
+    static constexpr int B_OFF = A_OFF + A_STAGES * DT_A_STRIDE;
     static constexpr int B_BYTES = (B_RESIDENT ? 10 : B_STAGES) * B_TILE;      // resident: the 9 taps of one chunk (<= 80 KB)
     static constexpr int BAR_OFF = B_OFF + B_BYTES;
     static constexpr int NBARS = 2 * A_STAGES + 2 * B_STAGES + 4 + 1;
@@ -135,7 +136,7 @@ direct_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                     const int st = (int)(acount % A_STAGES);
                     if (!mbar_wait_bounded(bar_aempty + 8 * st, (uint32_t)(((acount / A_STAGES) & 1) ^ 1), abort_flag, p.status, DT_W_A_EMPTY)) { ok = false; break; }
                     mbar_arrive_expect_tx(bar_afull + 8 * st, DT_A_BYTES);
-                    tma_load_4d(base + L::A_OFF + st * DT_A_BYTES, &tm_x, bar_afull + 8 * st, ch * 64, tx * DT_TW - p.pad, ty * DT_TH - p.pad, n);
+                    tma_load_4d(base + L::A_OFF + st * DT_A_STRIDE, &tm_x, bar_afull + 8 * st, ch * 64, tx * DT_TW - p.pad, ty * DT_TH - p.pad, n);
                     ++acount;
                     if (!B_RESIDENT) {
                         for (int tap = 0; tap < 9; ++tap) {
@@ -165,24 +166,30 @@ direct_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                     const int st = (int)(acount % A_STAGES);
                     if (!mbar_wait_bounded(bar_afull + 8 * st, (uint32_t)((acount / A_STAGES) & 1), abort_flag, p.status, DT_W_A_FULL)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_s = base + L::A_OFF + st * DT_A_BYTES;
+                    const uint32_t a_s = base + L::A_OFF + st * DT_A_STRIDE;
+                    // descriptors are built once per ring slot; per tap and K-step only a constant is added to the
+                    // 16-byte-unit start address in the low word (the single issuing lane is the critical path)
+                    const uint64_t a_desc0 = smem_desc_k128_sbo(a_s, DT_BOX_W * 128);
+#pragma unroll
                     for (int tap = 0; tap < 9; ++tap) {
-                        uint32_t b_s;
+                        uint64_t b_desc0;
                         int sb = 0;
                         if (B_RESIDENT) {
-                            b_s = base + L::B_OFF + (ch * 9 + tap) * L::B_TILE;
+                            b_desc0 = smem_desc_k128(base + L::B_OFF + ch * 9 * L::B_TILE) + (uint64_t)((tap * L::B_TILE) >> 4);
                         } else {
                             sb = (int)(bcount % B_STAGES);
                             if (!mbar_wait_bounded(bar_bfull + 8 * sb, (uint32_t)((bcount / B_STAGES) & 1), abort_flag, p.status, DT_W_B_FULL)) { ok = false; break; }
                             tc_fence_after();
-                            b_s = base + L::B_OFF + sb * L::B_TILE;
+                            b_desc0 = smem_desc_k128(base + L::B_OFF + sb * L::B_TILE);
                         }
-                        const int r = tap / 3, s = tap % 3;
-                        const uint32_t a_tap = a_s + (uint32_t)((r * DT_BOX_W + s) * 128);
+                        const uint64_t a_desc = a_desc0 + (uint64_t)((((tap / 3) * DT_BOX_W + (tap % 3)) * 128) >> 4);
 #pragma unroll
-                        for (int ks = 0; ks < 4; ++ks)
-                            tc_mma<false>(d_tmem, smem_desc_k128_sbo(a_tap + ks * 32, DT_BOX_W * 128), smem_desc_k128(b_s + ks * 32), p.idesc,
-                                          (ch | tap | ks) ? 1u : 0u);
+                        for (int ks = 0; ks < 4; ++ks) {
+                            if (tap == 0 && ks == 0)
+                                tc_mma<false>(d_tmem, a_desc, b_desc0, p.idesc, ch ? 1u : 0u);
+                            else
+                                tc_mma<false>(d_tmem, a_desc + (uint64_t)(ks * 2), b_desc0 + (uint64_t)(ks * 2), p.idesc, 1u);
+                        }
                         if (!B_RESIDENT) { tc_commit(bar_bempty + 8 * sb); ++bcount; }
                     }
                     if (!ok) break;
@@ -361,8 +368,8 @@ int launch_direct_tc(const wino_conv_desc& d, const Geometry& g, const void* x, 
     }
     if ((rc = make_map_k128(&tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, packed, d.c, d.k, d.k, 9, bn))) return rc;
     const bool resident = 9 * p.cchunks * bn * 128 <= 80 * 1024;
-    if (bn == 64) return resident ? run<64, 3, 2, true>(tm_x, tm_w, p, st) : run<64, 3, 6, false>(tm_x, tm_w, p, st);
-    return run<128, 3, 4, false>(tm_x, tm_w, p, st);
+    if (bn == 64) return resident ? run<64, 6, 2, true>(tm_x, tm_w, p, st) : run<64, 6, 6, false>(tm_x, tm_w, p, st);
+    return run<128, 6, 4, false>(tm_x, tm_w, p, st);
 }
 
 }  // namespace wino

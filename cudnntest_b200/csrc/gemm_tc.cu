@@ -130,10 +130,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant__
                     tc_fence_after();
                     const int left = p.cp - kc * KC;
                     const int ksteps = left >= KC ? KC / UMMA_K : (left + UMMA_K - 1) / UMMA_K;
-                    const uint32_t a_s = a_ring + stage * TC_A_BYTES, b_s = b_ring + stage * L::B_BYTES;
+                    // descriptors once per ring slot; a K-step adds 32 bytes = 2 sixteen-byte units to the start address
+                    const uint64_t a_desc = smem_desc_k128(a_ring + stage * TC_A_BYTES), b_desc = smem_desc_k128(b_ring + stage * L::B_BYTES);
+#pragma unroll 4
                     for (int ks = 0; ks < ksteps; ++ks)
-                        tc_mma<TF32>(d_tmem, smem_desc_k128(a_s + ks * 32), smem_desc_k128(b_s + ks * 32), p.idesc,
-                                     (kc | ks) ? 1u : 0u);
+                        tc_mma<TF32>(d_tmem, a_desc + (uint64_t)(ks * 2), b_desc + (uint64_t)(ks * 2), p.idesc, (kc | ks) ? 1u : 0u);
                     tc_commit(bar_empty + 8 * stage);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }

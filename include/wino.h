@@ -55,9 +55,11 @@ typedef struct wino_conv_desc {
     int dtype;                 /* WINO_FP32 / WINO_TF32 / WINO_BF16                                  */
     int operand;               /* WINO_BF16 only: format of the transformed operands; AUTO = F16 (FP16
                                   operands keep both tile sizes inside the 5e-3 tolerance)          */
-    int wino;                  /* output tile size m of F(m x m, 3x3): 2 or 4; 0 = 4                  */
+    int wino;                  /* output tile size m of F(m x m, 3x3): 2 or 4.  0 = the engine chooses:
+                                  F(4x4,3x3), except that thin NHWC layers of the tensor-core variants run
+                                  a direct tensor-core kernel (C <= 3; BF16 with C = 64 or 128)          */
     int relu, has_bias, pool2x2; /* epilogue fused into the output transform: y = pool(relu(conv+b)) */
-    int slab_images;           /* images transformed per pass; 0 = sized so a pass stays L2 resident */
+    int slab_images;           /* images transformed per pass; 0 = as many as fit a 2 GiB scratch       */
     int reserved;
 } wino_conv_desc;
 
@@ -87,7 +89,8 @@ int wino_filter_transform(const wino_conv_desc* d, const void* w, void* u, wino_
  * (comparison/wrapedConv_NCHW.cuh:335-492, wrapedConv_NHWC.cuh:24-112, wrapedConv_CHWN.cuh:16-82),
  * the six convLayoutTrans_X_to_Y (comparison/DataLayoutTrans.cuh:9-584) when layout_out differs, and
  * the separate bias / ReLU / pool passes of netTest/cudnn_test_0124/VGG_Batched/Network.h:456-519.
- * `u` comes from wino_filter_transform with the same descriptor.  bias: K floats or NULL. */
+ * `u` comes from wino_filter_transform with the same descriptor (it holds the transformed filters, or the
+ * repacked raw filters where the descriptor selects a direct kernel).  bias: K floats (16-byte aligned) or NULL. */
 int wino_conv_forward(const wino_conv_desc* d, const void* x, const void* u, const float* bias, void* y,
                       void* workspace, size_t workspace_bytes, wino_stream_t stream);
 
