@@ -12,8 +12,8 @@
 //     filter tap (r, s) is that same slot read through a shared-memory matrix descriptor that starts at pixel
 //     (r, s) of the box: 8-pixel row groups 2048 bytes apart, start address advanced by (16 r + s) * 128 bytes
 //     (the swizzle phase follows the address).  Nine taps x four K-steps of tcgen05.mma per chunk reuse one load;
-//   * filter tiles Wd[tap][K][Cp] are either resident in shared memory for the whole kernel (9 * chunks * BN rows
-//     <= 80 KB) or streamed through their own ring;
+//   * filter tiles Wd[tap][K][Cp] are either resident in shared memory for the whole kernel (C = 64: nine tiles) or
+//     streamed through their own ring;
 //   * epilogue warps read their accumulator lane (= pixel) from tensor memory, add bias, apply ReLU and, for
 //     block-ending layers, take the 2x2 max with two warp shuffles (the tile's pixel order puts the 2x2 window in
 //     lanes l, l^1, l^8, l^9), then store 16-byte vectors of the pixel's BN contiguous NHWC channels.
@@ -69,7 +69,7 @@ struct DtSmem {
     static constexpr int B_TILE = BN * 128;
     static constexpr int A_OFF = 0;
     static constexpr int B_OFF = A_OFF + A_STAGES * DT_A_STRIDE;
-    static constexpr int B_BYTES = (B_RESIDENT ? 10 : B_STAGES) * B_TILE;      // resident: the 9 taps of one chunk (<= 80 KB)
+    static constexpr int B_BYTES = (B_RESIDENT ? 9 : B_STAGES) * B_TILE;       // resident: the 9 taps of a single-chunk layer
     static constexpr int BAR_OFF = B_OFF + B_BYTES;
     static constexpr int NBARS = 2 * A_STAGES + 2 * B_STAGES + 4 + 1;
     static constexpr int SLOT_OFF = BAR_OFF + 8 * NBARS;
@@ -367,9 +367,10 @@ int launch_direct_tc(const wino_conv_desc& d, const Geometry& g, const void* x, 
         if ((rc = encode_tensor_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, x, dims, strides, box, true))) return rc;
     }
     if ((rc = make_map_k128(&tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, packed, d.c, d.k, d.k, 9, bn))) return rc;
-    const bool resident = 9 * p.cchunks * bn * 128 <= 80 * 1024;
+    // filters stay resident in shared memory when the layer has a single 64-channel chunk (C = 64)
+    const bool resident = p.cchunks == 1;
     if (bn == 64) return resident ? run<64, 6, 2, true>(tm_x, tm_w, p, st) : run<64, 6, 6, false>(tm_x, tm_w, p, st);
-    return run<128, 6, 4, false>(tm_x, tm_w, p, st);
+    return resident ? run<128, 3, 2, true>(tm_x, tm_w, p, st) : run<128, 6, 4, false>(tm_x, tm_w, p, st);
 }
 
 }  // namespace wino
