@@ -185,6 +185,23 @@ def test_full_size_config1_bf16(cb):
     assert rel_l2(y[:2], ref) <= TOL_L2
 
 
+@pytest.mark.parametrize("layout", ["NHWC", "CHWN"])
+@pytest.mark.parametrize("dtype,wino", [("bf16", 2), ("bf16", 4), ("fp32", 2), ("fp32", 4)])
+def test_full_size_config2(cb, layout, dtype, wino):
+    """BASELINE config 2: N=64, C=K=512, 28x28, F(2x2,3x3) and F(4x4,3x3), BF16 and FP32, NHWC and CHWN.  Two images
+    against the oracle; the whole batch through the property that images are independent (slab size 9 vs default)."""
+    n, c, h, k = 64, 512, 28, 512
+    x, wt, b = make_inputs(n, c, h, h, k, seed=0xC0DE0020)
+    y = run_conv(x, wt, b, layout, dtype=dtype, wino=wino, relu=True)
+    ref = oracle.conv_f64(x[:2], wt, bias=b, relu=True)
+    if dtype == "fp32":
+        assert maxrel(y[:2], ref) <= 1e-4
+    else:
+        assert rel_l2(y[:2], ref) <= TOL_L2
+    y2 = run_conv(x, wt, b, layout, dtype=dtype, wino=wino, relu=True, slab_images=9)
+    assert np.array_equal(y, y2)
+
+
 def test_full_size_config3_bf16_nchw(cb):
     """BASELINE config 3: N=128, C=K=512, 14x14, BF16, NCHW, bias+ReLU; four images vs the oracle."""
     n, c, h, k = 128, 512, 14, 512
