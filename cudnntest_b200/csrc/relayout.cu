@@ -35,10 +35,53 @@ __global__ void __launch_bounds__(256) transpose_batched_kernel(const T* __restr
     }
 }
 
+// 2-byte elements, even extents and strides: 64 x 64 element tiles moved as 4-byte words on both sides (a warp reads
+// 128 bytes along q and writes 128 bytes along r), the pairing is changed inside shared memory.
+__global__ void __launch_bounds__(256) transpose_batched_pairs_kernel(const uint16_t* __restrict__ in, uint16_t* __restrict__ out, int R,
+                                                                      int Q, int qtiles, long long sb_in, long long sr_in,
+                                                                      long long sb_out, long long sq_out) {
+    __shared__ uint16_t tile[64][66];
+    const int qt = blockIdx.x % qtiles;
+    const long long b = blockIdx.x / qtiles;
+    const int q0 = qt * 64, r0 = blockIdx.y * 64;
+    const int lx = threadIdx.x % 32, ly = threadIdx.x / 32;   // 32 x 8
+    const uint16_t* src = in + b * sb_in;
+    uint16_t* dst = out + b * sb_out;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int r = r0 + ly + 8 * i, q = q0 + 2 * lx;
+        if (r < R && q < Q) {
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(src + r * sr_in + q);
+            tile[ly + 8 * i][2 * lx] = (uint16_t)(w & 0xffffu);
+            tile[ly + 8 * i][2 * lx + 1] = (uint16_t)(w >> 16);
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int q = q0 + ly + 8 * i, r = r0 + 2 * lx;
+        if (r < R && q < Q) {
+            const uint32_t w = (uint32_t)tile[2 * lx][ly + 8 * i] | ((uint32_t)tile[2 * lx + 1][ly + 8 * i] << 16);
+            *reinterpret_cast<uint32_t*>(dst + q * sq_out + r) = w;
+        }
+    }
+}
+
 template <typename T>
 static int run_transpose(const void* in, void* out, long long B, long long R, long long Q, long long sb_in, long long sr_in,
                          long long sb_out, long long sq_out, cudaStream_t st) {
     if (B == 0 || R == 0 || Q == 0) return WINO_OK;
+    if (sizeof(T) == 2 && ((R | Q | sb_in | sr_in | sb_out | sq_out) & 1) == 0 && (((uintptr_t)in | (uintptr_t)out) & 3) == 0) {
+        const long long qt = (Q + 63) / 64, rt = (R + 63) / 64;
+        if (B * qt <= 0x7fffffffLL && rt <= 65535 && R <= 0x7fffffffLL && Q <= 0x7fffffffLL) {
+            dim3 grid((unsigned)(B * qt), (unsigned)rt);
+            count_launch();
+            transpose_batched_pairs_kernel<<<grid, 256, 0, st>>>((const uint16_t*)in, (uint16_t*)out, (int)R, (int)Q, (int)qt, sb_in, sr_in,
+                                                                  sb_out, sq_out);
+            WINO_CUDA_CHECK(cudaGetLastError());
+            return WINO_OK;
+        }
+    }
     const long long qtiles = (Q + 31) / 32, rtiles = (R + 31) / 32;
     if (B * qtiles > 0x7fffffffLL || rtiles > 65535 || R > 0x7fffffffLL || Q > 0x7fffffffLL)
         return fail(WINO_E_UNSUPPORTED, "relayout: tensor too large for one launch");
@@ -88,9 +131,102 @@ __global__ void __launch_bounds__(256) maxpool_kernel(const T* __restrict__ in, 
     out[idx] = from_float<T>(fmaxf(fmaxf(a, b), fmaxf(cc, d)));
 }
 
+template <typename T>
+__device__ __forceinline__ uint4 max16(uint4 a, uint4 b);
+template <>
+__device__ __forceinline__ uint4 max16<float>(uint4 a, uint4 b) {
+    return make_uint4(__float_as_uint(fmaxf(__uint_as_float(a.x), __uint_as_float(b.x))), __float_as_uint(fmaxf(__uint_as_float(a.y), __uint_as_float(b.y))),
+                      __float_as_uint(fmaxf(__uint_as_float(a.z), __uint_as_float(b.z))), __float_as_uint(fmaxf(__uint_as_float(a.w), __uint_as_float(b.w))));
+}
+template <>
+__device__ __forceinline__ uint4 max16<__nv_bfloat16>(uint4 a, uint4 b) {
+    uint4 r;
+    const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+    __nv_bfloat162* pr = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pr[i] = __hmax2(pa[i], pb[i]);
+    return r;
+}
+
+// Pool for layouts whose innermost dimension is not pooled (NHWC: c, CHWN: n): 16-byte vectors along it.
+// The tensor is viewed as [outer][H][W][inner] with inner a multiple of the vector length.
+template <typename T>
+__global__ void __launch_bounds__(256) maxpool_inner_vec_kernel(const T* __restrict__ in, T* __restrict__ out, int H, int W,
+                                                                long long inner_vecs, long long total_vecs) {
+    constexpr int VE = 16 / (int)sizeof(T);
+    const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= total_vecs) return;
+    const int PH = H / 2, PW = W / 2;
+    const long long iv = idx % inner_vecs;
+    long long r = idx / inner_vecs;
+    const int pw = (int)(r % PW); r /= PW;
+    const int ph = (int)(r % PH);
+    const long long outer = r / PH;
+    const long long inner = inner_vecs * VE;
+    const T* p = in + ((outer * H + 2 * ph) * W + 2 * pw) * inner + iv * VE;
+    const uint4 a = *reinterpret_cast<const uint4*>(p), b = *reinterpret_cast<const uint4*>(p + inner);
+    const uint4 c = *reinterpret_cast<const uint4*>(p + (long long)W * inner), d = *reinterpret_cast<const uint4*>(p + (long long)W * inner + inner);
+    *reinterpret_cast<uint4*>(out + idx * VE) = max16<T>(max16<T>(a, b), max16<T>(c, d));
+}
+
+// NCHW: the pooled dimension w is the contiguous one.  A thread produces VE adjacent outputs of one row from two
+// 16-byte vectors of each of the two input rows (W a multiple of 2*VE keeps every vector aligned).
+template <typename T>
+__global__ void __launch_bounds__(256) maxpool_nchw_vec_kernel(const T* __restrict__ in, T* __restrict__ out, int H, int W,
+                                                               long long total_vecs) {
+    constexpr int VE = 16 / (int)sizeof(T);
+    const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= total_vecs) return;
+    const int PH = H / 2, PWV = W / (2 * VE);
+    const int pv = (int)(idx % PWV);
+    long long r = idx / PWV;
+    const int ph = (int)(r % PH);
+    const long long plane = r / PH;
+    const T* p = in + (plane * H + 2 * ph) * W + (long long)pv * 2 * VE;
+    __align__(16) T r0[2 * VE], r1[2 * VE], o[VE];
+    *reinterpret_cast<uint4*>(r0) = *reinterpret_cast<const uint4*>(p);
+    *reinterpret_cast<uint4*>(r0 + VE) = *reinterpret_cast<const uint4*>(p + VE);
+    *reinterpret_cast<uint4*>(r1) = *reinterpret_cast<const uint4*>(p + W);
+    *reinterpret_cast<uint4*>(r1 + VE) = *reinterpret_cast<const uint4*>(p + W + VE);
+#pragma unroll
+    for (int e = 0; e < VE; ++e)
+        o[e] = from_float<T>(fmaxf(fmaxf(to_float<T>(r0[2 * e]), to_float<T>(r0[2 * e + 1])), fmaxf(to_float<T>(r1[2 * e]), to_float<T>(r1[2 * e + 1]))));
+    *reinterpret_cast<uint4*>(out + (plane * PH + ph) * (W / 2) + (long long)pv * VE) = *reinterpret_cast<const uint4*>(o);
+}
+
 int launch_maxpool(int layout, int n, int c, int h, int w, int dtype, const void* in, void* out, cudaStream_t st) {
     const long long total = (long long)n * c * (h / 2) * (w / 2);
     if (total == 0) return WINO_OK;
+    {
+        // NHWC = [n][H][W][c], CHWN = [c][H][W][n]
+        const int es = dtype == WINO_BF16 ? 2 : 4, ve = 16 / es;
+        const long long inner = layout == WINO_NHWC ? c : layout == WINO_CHWN ? n : 0;
+        if (layout == WINO_NCHW && w % (2 * ve) == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+            const long long vecs = total / ve, blocks = (vecs + 255) / 256;
+            if (blocks <= 0x7fffffffLL) {
+                count_launch();
+                if (dtype == WINO_BF16)
+                    maxpool_nchw_vec_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, h, w, vecs);
+                else
+                    maxpool_nchw_vec_kernel<float><<<(unsigned)blocks, 256, 0, st>>>((const float*)in, (float*)out, h, w, vecs);
+                WINO_CUDA_CHECK(cudaGetLastError());
+                return WINO_OK;
+            }
+        }
+        if (inner > 0 && inner % ve == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+            const long long vecs = total / ve, blocks = (vecs + 255) / 256;
+            if (blocks <= 0x7fffffffLL) {
+                count_launch();
+                if (dtype == WINO_BF16)
+                    maxpool_inner_vec_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, h, w, inner / ve, vecs);
+                else
+                    maxpool_inner_vec_kernel<float><<<(unsigned)blocks, 256, 0, st>>>((const float*)in, (float*)out, h, w, inner / ve, vecs);
+                WINO_CUDA_CHECK(cudaGetLastError());
+                return WINO_OK;
+            }
+        }
+    }
     const long long blocks = (total + 255) / 256;
     if (blocks > 0x7fffffffLL) return fail(WINO_E_UNSUPPORTED, "maxpool: tensor too large for one launch");
     count_launch();

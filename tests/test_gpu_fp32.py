@@ -154,26 +154,26 @@ def test_padding_zero(cb):
 @pytest.mark.parametrize("dst", LAYOUTS)
 def test_relayout_bit_exact(cb, src, dst):
     import torch
-    n, c, h, w = 3, 37, 9, 13
     rng = np.random.default_rng(1)
-    x = rng.standard_normal((n, c, h, w)).astype(np.float32)
-    for tdt in (torch.float32, torch.bfloat16):
-        xs = to_dev(oracle.to_layout(x, src), tdt)
-        out = cb.layout_convert(xs, src, dst, n, c, h, w)
-        ref = xs.float().cpu().numpy()
-        assert np.array_equal(oracle.from_layout(out.float().cpu().numpy(), dst), oracle.from_layout(ref, src))
+    for (n, c, h, w) in ((3, 37, 9, 13), (8, 72, 10, 14), (2, 130, 6, 66)):     # odd extents (scalar path) and even ones (paired path)
+        x = rng.standard_normal((n, c, h, w)).astype(np.float32)
+        for tdt in (torch.float32, torch.bfloat16):
+            xs = to_dev(oracle.to_layout(x, src), tdt)
+            out = cb.layout_convert(xs, src, dst, n, c, h, w)
+            ref = xs.float().cpu().numpy()
+            assert np.array_equal(oracle.from_layout(out.float().cpu().numpy(), dst), oracle.from_layout(ref, src))
 
 
 @pytest.mark.parametrize("layout", LAYOUTS)
 def test_maxpool_bit_exact(cb, layout):
     import torch
-    n, c, h, w = 2, 19, 10, 14
-    x = np.random.default_rng(2).standard_normal((n, c, h, w)).astype(np.float32)
-    for tdt in (torch.float32, torch.bfloat16):
-        xs = to_dev(oracle.to_layout(x, layout), tdt)
-        out = cb.maxpool2x2(xs, layout, n, c, h, w)
-        ref = oracle.maxpool2x2(xs.float().cpu().numpy(), layout)
-        assert np.array_equal(out.float().cpu().numpy(), ref)
+    for (n, c, h, w) in ((2, 19, 10, 14), (8, 24, 9, 11), (16, 64, 12, 6), (2, 5, 7, 32)):       # scalar and 16-byte-vector paths, odd H / W
+        x = np.random.default_rng(2).standard_normal((n, c, h, w)).astype(np.float32)
+        for tdt in (torch.float32, torch.bfloat16):
+            xs = to_dev(oracle.to_layout(x, layout), tdt)
+            out = cb.maxpool2x2(xs, layout, n, c, h, w)
+            ref = oracle.maxpool2x2(xs.float().cpu().numpy(), layout)
+            assert np.array_equal(out.float().cpu().numpy(), ref)
 
 
 def test_errors_are_reported(cb):
