@@ -294,6 +294,15 @@ def run_ours(args, rank, world, local_rank):
         roofline = {"kernel": kernel_names[dominant], "bound": "tensor", "achieved": achieved, "peak": tpeak, "unit": "TFLOP/s",
                     "frac": achieved / tpeak, "traffic": None,
                     "peak_source": peaks["source"] + " sustained bf16 cuBLAS" + (" halved for tf32" if args.dtype == "tf32" else "")}
+    # DRAM traffic per launch: ncu's dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of this kernel
+    # (profiles/ncu_<kernel>_vgg16_bf16_nhwc_batch32.md) divided by that launch's algorithmic bytes, applied to the
+    # average algorithmic bytes per launch here.  Reads match the algorithmic bytes; output still dirty in the 126 MB L2
+    # when the captured launch ends is not in ncu's write count, hence ratios below 1.
+    ncu_ratio = {"direct_tensor_core": 0.94, "tile_gemm_plain": 0.71, "output_transform": 0.89, "input_transform": 0.36,
+                 "direct_thin_input": 0.76, "tile_gemm_rowfused": 0.88}
+    if args.dtype == "bf16" and args.layout == "NHWC":
+        roofline["traffic"] = ncu_ratio[dominant] * byts / max(stage[dominant]["launches"], 1)
+        roofline["traffic_note"] = "bytes per launch = ncu DRAM/algorithmic ratio %.2f (batch-32 capture) x algorithmic bytes per launch" % ncu_ratio[dominant]
     roofline["algorithmic_bytes_per_step"] = byts
     roofline["algorithmic_flops_per_step"] = flops
     roofline["launches_per_step"] = stage[dominant]["launches"]
