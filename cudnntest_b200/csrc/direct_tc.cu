@@ -24,45 +24,11 @@
 #include "common.cuh"
 #include "ptx.cuh"
 #include "tcgen05.cuh"
+#include "direct_tc.cuh"
 
 namespace wino {
 
 namespace {
-
-constexpr int DT_TW = 8, DT_TH = 16;                 // output tile
-constexpr int DT_BOX_W = DT_TW + 2, DT_BOX_H = DT_TH + 2;   // halo box: 10 x 18 pixels
-constexpr int DT_A_BYTES = DT_BOX_W * DT_BOX_H * 128;                      // bytes one halo box brings in
-constexpr int DT_A_STRIDE = (DT_A_BYTES + 1023) / 1024 * 1024;            // ring slots stay 1 KiB aligned
-constexpr int DT_EPI_WARPS = 8;                      // two warps per tensor-memory lane quarter, each takes half the filter columns
-constexpr int DT_THREADS = 64 + 32 * DT_EPI_WARPS;
-
-enum DtWaitCode { DT_W_A_EMPTY = 41, DT_W_A_FULL = 42, DT_W_B_EMPTY = 43, DT_W_B_FULL = 44, DT_W_T_EMPTY = 45, DT_W_T_FULL = 46,
-                  DT_W_B_RESIDENT = 47 };
-
-struct DtParams {
-    const float* bias;
-    __nv_bfloat16* y;
-    int N, OH, OW, K, pad;
-    int PH, PW;                  // stored output size (after the optional pool)
-    int tiles_x, tiles_y, nblocks, cchunks;
-    int relu, pool;
-    uint32_t idesc;
-    int* status;
-};
-
-// K-major, 128-byte swizzle, 8-row groups `sbo` bytes apart.  The start address may be any 128-byte row of a
-// swizzled box: the MMA unit derives the swizzle phase of every row from its shared-memory address (measured: the
-// descriptor's base-offset field must stay 0 for starts that are not 1 KiB aligned, the results are wrong with
-// base offset = row phase).
-__device__ __forceinline__ uint64_t smem_desc_k128_sbo(uint32_t saddr, uint32_t sbo) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(sbo >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
 
 template <int BN, int A_STAGES, int B_STAGES, bool B_RESIDENT>
 struct DtSmem {
@@ -327,7 +293,8 @@ int run(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const DtParams& p, cud
 bool direct_tc_applies(const wino_conv_desc& d) {
     static const int mode = [] { const char* e = getenv("WINO_DIRECT_TC"); return e ? atoi(e) : 1; }();
     if (mode == 0) return false;
-    return d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC && d.dtype == WINO_BF16 && d.c % 64 == 0 && d.c <= 128 &&
+    static const int max_c = [] { const char* e = getenv("WINO_DIRECT_TC_MAXC"); return e ? atoi(e) : 128; }();
+    return d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC && d.dtype == WINO_BF16 && d.c % 64 == 0 && d.c <= max_c &&
            d.k % 8 == 0 && (d.wino == 0);
 }
 
@@ -346,6 +313,7 @@ int launch_direct_tc_pack(const wino_conv_desc& d, const void* w, void* packed, 
 int launch_direct_tc(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,
                      cudaStream_t st) {
     if (d.n == 0) return WINO_OK;
+    if (direct_tc2_applies(d)) return launch_direct_tc2(d, g, x, packed, bias, y, st);
     if (((uintptr_t)x | (uintptr_t)packed | (uintptr_t)y | (d.has_bias ? (uintptr_t)bias : 0)) & 15)
         return fail(WINO_E_BADARG, "direct conv: buffers (and the bias) must be 16-byte aligned");
     DtParams p;

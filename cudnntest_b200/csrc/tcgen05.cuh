@@ -25,6 +25,33 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// ---- CTA-pair (cta_group::2) forms: one allocation / one MMA spans the tensor memory of both CTAs of a cluster of two.
+// The allocation and the release are executed by the same warp index in BOTH CTAs.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t slot_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// arrive on the mbarrier at this shared-memory offset in every CTA of cta_mask once the pair MMAs issued so far are done
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"(cta_mask)
+                 : "memory");
+}
+// D (256 x N: rows 0..127 in the leader's tensor memory, 128..255 in the peer's) += A (each CTA's own 128 rows) x B
+// (each CTA holds N/2 of the N rows); issued by one thread of the leader CTA, descriptors are CTA-relative.
+__device__ __forceinline__ void tc_mma_pair_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 bytes apart, 8-row groups
 // 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_k128(uint32_t saddr) {
@@ -34,6 +61,20 @@ __device__ __forceinline__ uint64_t smem_desc_k128(uint32_t saddr) {
     d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset between 8-row groups
     d |= (uint64_t)1 << 46;                    // descriptor version for tcgen05
     d |= (uint64_t)2 << 61;                    // 128-byte swizzle
+    return d;
+}
+
+// Same, with the 8-row groups `sbo` bytes apart.  The start address may be any 128-byte row of a swizzled box: the
+// MMA unit derives the swizzle phase of every row from its shared-memory address (measured: the descriptor's
+// base-offset field must stay 0 for starts that are not 1 KiB aligned; with base offset = row phase the results
+// are wrong).
+__device__ __forceinline__ uint64_t smem_desc_k128_sbo(uint32_t saddr, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(sbo >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
     return d;
 }
 
@@ -107,8 +148,8 @@ inline int make_map_k128(CUtensorMap* map, CUtensorMapDataType dt, int es, const
     return encode_tensor_map(map, dt, 3, ptr, dims, strides, box, true);
 }
 
-// tcgen05 instruction descriptor: FP32 accumulate, K-major A and B, M = 128, N = bn
-inline uint32_t make_idesc(int operand, int bn) {
+// tcgen05 instruction descriptor: FP32 accumulate, K-major A and B, M = bm (128; 256 for a CTA-pair MMA), N = bn
+inline uint32_t make_idesc(int operand, int bn, int bm = TC_BM) {
     const uint32_t fmt = operand == OP_TF32 ? 2u : operand == OP_BF16 ? 1u : 0u;  // kind::f16: 0 = F16, 1 = BF16
     uint32_t d = 0;
     d |= 1u << 4;                      // accumulator format: F32
@@ -116,7 +157,7 @@ inline uint32_t make_idesc(int operand, int bn) {
     d |= fmt << 10;                    // B format
     /* bits 13, 14: no negation; bits 15, 16: A and B are K-major */
     d |= (uint32_t)(bn >> 3) << 17;    // N / 8
-    d |= (uint32_t)(TC_BM >> 4) << 24; // M / 16
+    d |= (uint32_t)(bm >> 4) << 24;    // M / 16
     return d;
 }
 
