@@ -84,6 +84,7 @@ __global__ void __launch_bounds__(128) direct_small_c_kernel(const DCArgs a) {
     __shared__ __align__(8) unsigned long long bar_storage;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
+    __shared__ __align__(16) float bias_s[64];
 
     const int tid = threadIdx.x, warp = tid / 32;
     const int k0 = blockIdx.y * 64;
@@ -95,6 +96,11 @@ __global__ void __launch_bounds__(128) direct_small_c_kernel(const DCArgs a) {
         mbar_fence_init();
     }
     if (warp == 0) tmem_alloc(smem_u32(&tmem_slot), 64);
+    if (tid < 64) bias_s[tid] = (a.bias && k0 + tid < a.K) ? __ldg(a.bias + k0 + tid) : 0.f;
+    // dense NHWC output with a whole, 16-byte aligned block of 64 filters: pixels are consecutive 2*K-byte (4*K) rows
+    const bool dense_nhwc = !a.n_fastest && a.sy.c == 1 && a.sy.w == a.K && a.sy.h == (long long)a.ow * a.K &&
+                            a.sy.n == (long long)a.oh * a.ow * a.K && k0 + 64 <= a.K &&
+                            ((reinterpret_cast<uintptr_t>(a.y) | (uintptr_t)(a.K * sizeof(TOut)) | (uintptr_t)(k0 * sizeof(TOut))) & 15) == 0;
 
     // filter tile: row kf = packed filter row k0 + kf (32 operand values, see pack_direct_filters), zero beyond K
     if (tid < 64) {
@@ -174,7 +180,57 @@ __global__ void __launch_bounds__(128) direct_small_c_kernel(const DCArgs a) {
         tmem_ld_wait();
         tc_fence_before();
         __syncthreads();             // accumulator and operand tile may be overwritten by the next tile from here on
-        if (valid) {
+        if (dense_nhwc) {
+            // Each lane holds one pixel's 64 outputs.  Stored straight from there, one 16-byte store instruction of a warp
+            // touches 32 different 128-byte lines; instead the warp turns its 32 x 128-byte block around in its own rows
+            // of the operand tile (free once the MMA has completed, chunk index XOR row to stay conflict-free) so that
+            // eight consecutive lanes write one pixel's 128 contiguous bytes: four full lines per instruction.
+            constexpr int PER = 16 / (int)sizeof(TOut);          // outputs per 16-byte chunk
+            constexpr int PASSES = 64 / (8 * PER);               // 128 bytes of a pixel per pass
+            uint8_t* wtile = a_tile + warp * 32 * 128;
+            const int lane = tid & 31;
+            const long long p0 = tile * 128 + warp * 32;
+#pragma unroll
+            for (int pass = 0; pass < PASSES; ++pass) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    float o[PER];
+                    const float4* bp = reinterpret_cast<const float4*>(bias_s + pass * 8 * PER + c * PER);
+#pragma unroll
+                    for (int q = 0; q < PER / 4; ++q) {
+                        const float4 b4 = bp[q];
+                        const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int kk = pass * 8 * PER + c * PER + q * 4 + e;
+                            const float val = __uint_as_float(kk < 32 ? r0[kk] : r1[kk - 32]) + bb[e];
+                            o[q * 4 + e] = a.relu ? fmaxf(val, 0.f) : val;
+                        }
+                    }
+                    uint32_t wds[4];
+                    if constexpr (sizeof(TOut) == 2) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(o[2 * e], o[2 * e + 1]);
+                            wds[e] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) wds[e] = __float_as_uint(o[e]);
+                    }
+                    *reinterpret_cast<uint4*>(wtile + lane * 128 + ((c ^ (lane & 7)) << 4)) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+                }
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int j = i * 4 + (lane >> 3), cc = lane & 7;
+                    const uint4 v4 = *reinterpret_cast<const uint4*>(wtile + j * 128 + ((cc ^ (j & 7)) << 4));
+                    if (p0 + j < a.pixels)
+                        *reinterpret_cast<uint4*>(yout + (p0 + j) * a.K + k0 + pass * 8 * PER + cc * PER) = v4;
+                }
+                __syncwarp();
+            }
+        } else if (valid) {
             TOut* yp = yout + n * a.sy.n + oy * a.sy.h + ox * a.sy.w;
             if (a.sy.c == 1 && k0 + 64 <= a.K && (reinterpret_cast<uintptr_t>(yp + k0) & 15) == 0) {
                 // filters contiguous (NHWC): 16-byte stores

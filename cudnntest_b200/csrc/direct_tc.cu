@@ -86,13 +86,14 @@ direct_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     const long long step = B_RESIDENT ? (long long)(gridDim.x / p.nblocks) * p.nblocks : gridDim.x;
 
     if (warp == 0) {
-        if (lane == 0) {
+        {   // the whole warp walks the rings (warp-uniform addresses); one elected lane issues the copies
+            const bool issuer = elect_one();
             bool ok = true;
             if (B_RESIDENT) {       // all taps and chunks of this CTA's filter block, once
-                mbar_arrive_expect_tx(bar_bres, (uint32_t)(9 * p.cchunks * L::B_TILE));
+                if (issuer) mbar_arrive_expect_tx(bar_bres, (uint32_t)(9 * p.cchunks * L::B_TILE));
                 for (int ch = 0; ch < p.cchunks; ++ch)
                     for (int tap = 0; tap < 9; ++tap)
-                        tma_load_3d(base + L::B_OFF + (ch * 9 + tap) * L::B_TILE, &tm_w, bar_bres, ch * 64, my_nb * BN, tap);
+                        if (issuer) tma_load_3d(base + L::B_OFF + (ch * 9 + tap) * L::B_TILE, &tm_w, bar_bres, ch * 64, my_nb * BN, tap);
             }
             unsigned long long acount = 0, bcount = 0;
             for (long long t = first; ok && t < total; t += step) {
@@ -100,37 +101,38 @@ direct_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                 decode(t, n, ty, tx, nb);
                 for (int ch = 0; ok && ch < p.cchunks; ++ch) {
                     const int st = (int)(acount % A_STAGES);
-                    if (!mbar_wait_bounded(bar_aempty + 8 * st, (uint32_t)(((acount / A_STAGES) & 1) ^ 1), abort_flag, p.status, DT_W_A_EMPTY)) { ok = false; break; }
-                    mbar_arrive_expect_tx(bar_afull + 8 * st, DT_A_BYTES);
-                    tma_load_4d(base + L::A_OFF + st * DT_A_STRIDE, &tm_x, bar_afull + 8 * st, ch * 64, tx * DT_TW - p.pad, ty * DT_TH - p.pad, n);
+                    if (!mbar_wait_warp(bar_aempty + 8 * st, (uint32_t)(((acount / A_STAGES) & 1) ^ 1), abort_flag, p.status, DT_W_A_EMPTY)) { ok = false; break; }
+                    if (issuer) mbar_arrive_expect_tx(bar_afull + 8 * st, DT_A_BYTES);
+                    if (issuer) tma_load_4d(base + L::A_OFF + st * DT_A_STRIDE, &tm_x, bar_afull + 8 * st, ch * 64, tx * DT_TW - p.pad, ty * DT_TH - p.pad, n);
                     ++acount;
                     if (!B_RESIDENT) {
                         for (int tap = 0; tap < 9; ++tap) {
                             const int sb = (int)(bcount % B_STAGES);
-                            if (!mbar_wait_bounded(bar_bempty + 8 * sb, (uint32_t)(((bcount / B_STAGES) & 1) ^ 1), abort_flag, p.status, DT_W_B_EMPTY)) { ok = false; break; }
-                            mbar_arrive_expect_tx(bar_bfull + 8 * sb, L::B_TILE);
-                            tma_load_3d(base + L::B_OFF + sb * L::B_TILE, &tm_w, bar_bfull + 8 * sb, ch * 64, nb * BN, tap);
+                            if (!mbar_wait_warp(bar_bempty + 8 * sb, (uint32_t)(((bcount / B_STAGES) & 1) ^ 1), abort_flag, p.status, DT_W_B_EMPTY)) { ok = false; break; }
+                            if (issuer) mbar_arrive_expect_tx(bar_bfull + 8 * sb, L::B_TILE);
+                            if (issuer) tma_load_3d(base + L::B_OFF + sb * L::B_TILE, &tm_w, bar_bfull + 8 * sb, ch * 64, nb * BN, tap);
                             ++bcount;
                         }
                     }
                 }
             }
-            if (!ok) drain_after_abort();
+            if (!ok && issuer) drain_after_abort();
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        {   // warp-uniform loop, one elected lane issues: from a single-lane branch every tcgen05.mma cost its thread tens of cycles
+            const bool issuer = elect_one();
             bool ok = true;
-            if (B_RESIDENT) ok = mbar_wait_bounded(bar_bres, 0, abort_flag, p.status, DT_W_B_RESIDENT);
+            if (B_RESIDENT) ok = mbar_wait_warp(bar_bres, 0, abort_flag, p.status, DT_W_B_RESIDENT);
             unsigned long long acount = 0, bcount = 0;
             int as = 0;
             uint32_t aphase = 0;
             for (long long t = first; ok && t < total; t += step) {
-                if (!mbar_wait_bounded(bar_tempty + 8 * as, aphase ^ 1, abort_flag, p.status, DT_W_T_EMPTY)) { ok = false; break; }
+                if (!mbar_wait_warp(bar_tempty + 8 * as, aphase ^ 1, abort_flag, p.status, DT_W_T_EMPTY)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(as * BN);
                 for (int ch = 0; ok && ch < p.cchunks; ++ch) {
                     const int st = (int)(acount % A_STAGES);
-                    if (!mbar_wait_bounded(bar_afull + 8 * st, (uint32_t)((acount / A_STAGES) & 1), abort_flag, p.status, DT_W_A_FULL)) { ok = false; break; }
+                    if (!mbar_wait_warp(bar_afull + 8 * st, (uint32_t)((acount / A_STAGES) & 1), abort_flag, p.status, DT_W_A_FULL)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_s = base + L::A_OFF + st * DT_A_STRIDE;
                     // descriptors are built once per ring slot; per tap and K-step only a constant is added to the
@@ -144,7 +146,7 @@ direct_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                             b_desc0 = smem_desc_k128(base + L::B_OFF + ch * 9 * L::B_TILE) + (uint64_t)((tap * L::B_TILE) >> 4);
                         } else {
                             sb = (int)(bcount % B_STAGES);
-                            if (!mbar_wait_bounded(bar_bfull + 8 * sb, (uint32_t)((bcount / B_STAGES) & 1), abort_flag, p.status, DT_W_B_FULL)) { ok = false; break; }
+                            if (!mbar_wait_warp(bar_bfull + 8 * sb, (uint32_t)((bcount / B_STAGES) & 1), abort_flag, p.status, DT_W_B_FULL)) { ok = false; break; }
                             tc_fence_after();
                             b_desc0 = smem_desc_k128(base + L::B_OFF + sb * L::B_TILE);
                         }
@@ -152,17 +154,17 @@ direct_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 #pragma unroll
                         for (int ks = 0; ks < 4; ++ks) {
                             if (tap == 0 && ks == 0)
-                                tc_mma<false>(d_tmem, a_desc, b_desc0, p.idesc, ch ? 1u : 0u);
+                                { if (issuer) tc_mma<false>(d_tmem, a_desc, b_desc0, p.idesc, ch ? 1u : 0u); }
                             else
-                                tc_mma<false>(d_tmem, a_desc + (uint64_t)(ks * 2), b_desc0 + (uint64_t)(ks * 2), p.idesc, 1u);
+                                { if (issuer) tc_mma<false>(d_tmem, a_desc + (uint64_t)(ks * 2), b_desc0 + (uint64_t)(ks * 2), p.idesc, 1u); }
                         }
-                        if (!B_RESIDENT) { tc_commit(bar_bempty + 8 * sb); ++bcount; }
+                        if (!B_RESIDENT) { if (issuer) tc_commit(bar_bempty + 8 * sb); ++bcount; }
                     }
                     if (!ok) break;
-                    tc_commit(bar_aempty + 8 * st);
+                    if (issuer) tc_commit(bar_aempty + 8 * st);
                     ++acount;
                 }
-                if (ok) tc_commit(bar_tfull + 8 * as);
+                if (ok && issuer) tc_commit(bar_tfull + 8 * as);
                 as ^= 1;
                 if (as == 0) aphase ^= 1;
             }
@@ -293,9 +295,15 @@ int run(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const DtParams& p, cud
 bool direct_tc_applies(const wino_conv_desc& d) {
     static const int mode = [] { const char* e = getenv("WINO_DIRECT_TC"); return e ? atoi(e) : 1; }();
     if (mode == 0) return false;
-    static const int max_c = [] { const char* e = getenv("WINO_DIRECT_TC_MAXC"); return e ? atoi(e) : 128; }();
-    return d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC && d.dtype == WINO_BF16 && d.c % 64 == 0 && d.c <= max_c &&
-           d.k % 8 == 0 && (d.wino == 0);
+    // WINO_DIRECT_TC_MAXC forces the channel limit; by default the choice follows what was measured on B200 (batch 256):
+    // up to 256 input channels the direct kernel beats the three-kernel Winograd pipeline (whose transform-domain
+    // buffers are HBM-bound); at 512 channels Winograd's 4x fewer multiplies win, except on small images
+    // (14 x 14) where its tile GEMMs are too small to fill the machine.
+    static const int max_c = [] { const char* e = getenv("WINO_DIRECT_TC_MAXC"); return e ? atoi(e) : -1; }();
+    if (!(d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC && d.dtype == WINO_BF16 && d.c % 64 == 0 && d.k % 8 == 0 && d.wino == 0))
+        return false;
+    if (max_c >= 0) return d.c <= max_c;
+    return d.c <= 256 || (long long)d.h * d.w < 28 * 28;
 }
 
 size_t direct_tc_filter_bytes(const wino_conv_desc& d) { return (size_t)9 * d.k * d.c * 2; }

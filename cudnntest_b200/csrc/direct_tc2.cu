@@ -98,15 +98,16 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     };
 
     if (warp == 0) {
-        if (lane == 0) {
+        {   // the whole warp walks the rings (warp-uniform addresses); one elected lane issues the copies
+            const bool issuer = elect_one();
             bool ok = true;
             const uint32_t filter_row0 = (uint32_t)(rank * (BN / 2));
             if (B_RESIDENT) {       // this CTA's half of all taps and chunks of the pair's filter block, once
-                if (rank == 0) mbar_arrive_expect_tx(bar_bres, (uint32_t)(2 * 9 * p.cchunks * L::B_TILE));
+                if (rank == 0 && issuer) mbar_arrive_expect_tx(bar_bres, (uint32_t)(2 * 9 * p.cchunks * L::B_TILE));
                 const uint32_t bres_leader = mapa_shared(bar_bres, 0);
                 for (int ch = 0; ch < p.cchunks; ++ch)
                     for (int tap = 0; tap < 9; ++tap)
-                        tma_load_3d_pair(base + L::B_OFF + (ch * 9 + tap) * L::B_TILE, &tm_w, bres_leader, ch * 64,
+                        if (issuer) tma_load_3d_pair(base + L::B_OFF + (ch * 9 + tap) * L::B_TILE, &tm_w, bres_leader, ch * 64,
                                          my_nb * BN + filter_row0, tap);
             }
             unsigned long long acount = 0, bcount = 0;
@@ -117,9 +118,9 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         int n, ty, tx; bool valid;
                         decode(u, mt, n, ty, tx, nb, valid);
                         const int st = (int)(acount % A_STAGES);
-                        if (!mbar_wait_bounded(bar_aempty + 8 * st, (uint32_t)(((acount / A_STAGES) & 1) ^ 1), abort_flag, p.status, DT_W_A_EMPTY)) { ok = false; break; }
-                        if (rank == 0) mbar_arrive_expect_tx(bar_afull + 8 * st, 2 * DT_A_BYTES);
-                        tma_load_4d_pair(base + L::A_OFF + st * DT_A_STRIDE, &tm_x, mapa_shared(bar_afull + 8 * st, 0), ch * 64,
+                        if (!mbar_wait_warp(bar_aempty + 8 * st, (uint32_t)(((acount / A_STAGES) & 1) ^ 1), abort_flag, p.status, DT_W_A_EMPTY)) { ok = false; break; }
+                        if (rank == 0 && issuer) mbar_arrive_expect_tx(bar_afull + 8 * st, 2 * DT_A_BYTES);
+                        if (issuer) tma_load_4d_pair(base + L::A_OFF + st * DT_A_STRIDE, &tm_x, mapa_shared(bar_afull + 8 * st, 0), ch * 64,
                                          tx * DT_TW - p.pad, ty * DT_TH - p.pad, n);
                         ++acount;
                     }
@@ -127,26 +128,30 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     if (!B_RESIDENT) {
                         for (int tap = 0; tap < 9; ++tap) {
                             const int sb = (int)(bcount % B_STAGES);
-                            if (!mbar_wait_bounded(bar_bempty + 8 * sb, (uint32_t)(((bcount / B_STAGES) & 1) ^ 1), abort_flag, p.status, DT_W_B_EMPTY)) { ok = false; break; }
-                            if (rank == 0) mbar_arrive_expect_tx(bar_bfull + 8 * sb, 2 * L::B_TILE);
-                            tma_load_3d_pair(base + L::B_OFF + sb * L::B_TILE, &tm_w, mapa_shared(bar_bfull + 8 * sb, 0), ch * 64,
+                            if (!mbar_wait_warp(bar_bempty + 8 * sb, (uint32_t)(((bcount / B_STAGES) & 1) ^ 1), abort_flag, p.status, DT_W_B_EMPTY)) { ok = false; break; }
+                            if (rank == 0 && issuer) mbar_arrive_expect_tx(bar_bfull + 8 * sb, 2 * L::B_TILE);
+                            if (issuer) tma_load_3d_pair(base + L::B_OFF + sb * L::B_TILE, &tm_w, mapa_shared(bar_bfull + 8 * sb, 0), ch * 64,
                                              nb * BN + filter_row0, tap);
                             ++bcount;
                         }
                     }
                 }
             }
-            if (!ok) drain_after_abort();
+            if (!ok && issuer) drain_after_abort();
         }
     } else if (warp == 1) {
-        if (lane == 0 && rank == 0) {
+        // MMA issue (leader CTA only).  The whole warp runs the loop so that descriptors and addresses stay warp-uniform
+        // values (issuing from a single-lane branch instead cost tens of cycles per tcgen05.mma, more than a 64-filter
+        // MMA takes); one elected lane issues the tcgen05 instructions.
+        if (rank == 0) {
+            const bool issuer = elect_one();
             bool ok = true;
-            if (B_RESIDENT) ok = mbar_wait_bounded(bar_bres, 0, abort_flag, p.status, DT_W_B_RESIDENT);
+            if (B_RESIDENT) ok = mbar_wait_warp(bar_bres, 0, abort_flag, p.status, DT_W_B_RESIDENT);
             unsigned long long acount = 0, bcount = 0;
             int as = 0;
             uint32_t aphase = 0;
             for (long long u = first; ok && u < total; u += step) {
-                if (!mbar_wait_bounded(bar_tempty + 8 * as, aphase ^ 1, abort_flag, p.status, DT_W_T_EMPTY)) { ok = false; break; }
+                if (!mbar_wait_warp(bar_tempty + 8 * as, aphase ^ 1, abort_flag, p.status, DT_W_T_EMPTY)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(as * MT * BN);
                 for (int ch = 0; ok && ch < p.cchunks; ++ch) {
@@ -154,7 +159,7 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
                         const int st = (int)((acount + mt) % A_STAGES);
-                        if (!mbar_wait_bounded(bar_afull + 8 * st, (uint32_t)(((acount + mt) / A_STAGES) & 1), abort_flag, p.status, DT_W_A_FULL)) { ok = false; break; }
+                        if (!mbar_wait_warp(bar_afull + 8 * st, (uint32_t)(((acount + mt) / A_STAGES) & 1), abort_flag, p.status, DT_W_A_FULL)) { ok = false; break; }
                         a_desc0[mt] = smem_desc_k128_sbo(base + L::A_OFF + st * DT_A_STRIDE, DT_BOX_W * 128);
                     }
                     if (!ok) break;
@@ -167,7 +172,7 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                             b_desc0 = smem_desc_k128(base + L::B_OFF + ch * 9 * L::B_TILE) + (uint64_t)((tap * L::B_TILE) >> 4);
                         } else {
                             sb = (int)(bcount % B_STAGES);
-                            if (!mbar_wait_bounded(bar_bfull + 8 * sb, (uint32_t)((bcount / B_STAGES) & 1), abort_flag, p.status, DT_W_B_FULL)) { ok = false; break; }
+                            if (!mbar_wait_warp(bar_bfull + 8 * sb, (uint32_t)((bcount / B_STAGES) & 1), abort_flag, p.status, DT_W_B_FULL)) { ok = false; break; }
                             tc_fence_after();
                             b_desc0 = smem_desc_k128(base + L::B_OFF + sb * L::B_TILE);
                         }
@@ -178,19 +183,19 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 #pragma unroll
                             for (int ks = 0; ks < 4; ++ks) {
                                 if (tap == 0 && ks == 0)
-                                    tc_mma_pair_f16(d_tmem + mt * BN, a_desc, b_desc0, p.idesc, ch ? 1u : 0u);
+                                    { if (issuer) tc_mma_pair_f16(d_tmem + mt * BN, a_desc, b_desc0, p.idesc, ch ? 1u : 0u); }
                                 else
-                                    tc_mma_pair_f16(d_tmem + mt * BN, a_desc + (uint64_t)(ks * 2), b_desc0 + (uint64_t)(ks * 2), p.idesc, 1u);
+                                    { if (issuer) tc_mma_pair_f16(d_tmem + mt * BN, a_desc + (uint64_t)(ks * 2), b_desc0 + (uint64_t)(ks * 2), p.idesc, 1u); }
                             }
                         }
-                        if (!B_RESIDENT) { tc_commit_pair(bar_bempty + 8 * sb, 3); ++bcount; }
+                        if (!B_RESIDENT) { if (issuer) tc_commit_pair(bar_bempty + 8 * sb, 3); ++bcount; }
                     }
                     if (!ok) break;
 #pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) tc_commit_pair(bar_aempty + 8 * (int)((acount + mt) % A_STAGES), 3);
+                    for (int mt = 0; mt < MT; ++mt) { if (issuer) tc_commit_pair(bar_aempty + 8 * (int)((acount + mt) % A_STAGES), 3); }
                     acount += MT;
                 }
-                if (ok) tc_commit_pair(bar_tfull + 8 * as, 3);
+                if (ok && issuer) tc_commit_pair(bar_tfull + 8 * as, 3);
                 if (++as == ACC) { as = 0; aphase ^= 1; }
             }
         }

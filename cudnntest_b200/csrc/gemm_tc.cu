@@ -98,7 +98,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant__
     const long long total = (long long)p.batches * p.mblocks * p.nblocks;
 
     if (warp == 0) {
-        if (lane == 0) {
+        {   // the whole warp walks the ring (warp-uniform addresses); one elected lane issues the copies
+            const bool issuer = elect_one();
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -107,26 +108,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant__
                 const int mb = (int)((tile / p.nblocks) % p.mblocks);
                 const int xi = (int)(tile / ((long long)p.nblocks * p.mblocks));
                 for (int kc = 0; kc < p.kchunks; ++kc) {
-                    if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, TC_WAIT_EMPTY)) { ok = false; break; }
-                    mbar_arrive_expect_tx(bar_full + 8 * stage, TC_A_BYTES + L::B_BYTES);
-                    tma_load_3d(a_ring + stage * TC_A_BYTES, &tm_v, bar_full + 8 * stage, kc * KC, mb * TC_BM, xi);
-                    tma_load_3d(b_ring + stage * L::B_BYTES, &tm_u, bar_full + 8 * stage, kc * KC, nb * BN, xi);
+                    if (!mbar_wait_warp(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, TC_WAIT_EMPTY)) { ok = false; break; }
+                    if (issuer) {
+                        mbar_arrive_expect_tx(bar_full + 8 * stage, TC_A_BYTES + L::B_BYTES);
+                        tma_load_3d(a_ring + stage * TC_A_BYTES, &tm_v, bar_full + 8 * stage, kc * KC, mb * TC_BM, xi);
+                        tma_load_3d(b_ring + stage * L::B_BYTES, &tm_u, bar_full + 8 * stage, kc * KC, nb * BN, xi);
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
-            if (!ok) drain_after_abort();
+            if (!ok && issuer) drain_after_abort();
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        {   // warp-uniform loop, one elected lane issues: from a single-lane branch every tcgen05.mma cost its thread tens of cycles
+            const bool issuer = elect_one();
             int stage = 0, as = 0;
             uint32_t phase = 0, aphase = 0;
             bool ok = true;
             for (long long tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
-                if (!mbar_wait_bounded(bar_tempty + 8 * as, aphase ^ 1, abort_flag, p.status, TC_WAIT_TMEM_EMPTY)) { ok = false; break; }
+                if (!mbar_wait_warp(bar_tempty + 8 * as, aphase ^ 1, abort_flag, p.status, TC_WAIT_TMEM_EMPTY)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(as * BN);
                 for (int kc = 0; kc < p.kchunks; ++kc) {
-                    if (!mbar_wait_bounded(bar_full + 8 * stage, phase, abort_flag, p.status, TC_WAIT_FULL)) { ok = false; break; }
+                    if (!mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, p.status, TC_WAIT_FULL)) { ok = false; break; }
                     tc_fence_after();
                     const int left = p.cp - kc * KC;
                     const int ksteps = left >= KC ? KC / UMMA_K : (left + UMMA_K - 1) / UMMA_K;
@@ -134,11 +138,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant__
                     const uint64_t a_desc = smem_desc_k128(a_ring + stage * TC_A_BYTES), b_desc = smem_desc_k128(b_ring + stage * L::B_BYTES);
 #pragma unroll 4
                     for (int ks = 0; ks < ksteps; ++ks)
-                        tc_mma<TF32>(d_tmem, a_desc + (uint64_t)(ks * 2), b_desc + (uint64_t)(ks * 2), p.idesc, (kc | ks) ? 1u : 0u);
-                    tc_commit(bar_empty + 8 * stage);
+                        if (issuer) tc_mma<TF32>(d_tmem, a_desc + (uint64_t)(ks * 2), b_desc + (uint64_t)(ks * 2), p.idesc, (kc | ks) ? 1u : 0u);
+                    if (issuer) tc_commit(bar_empty + 8 * stage);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
-                if (ok) tc_commit(bar_tfull + 8 * as);
+                if (ok && issuer) tc_commit(bar_tfull + 8 * as);
                 as ^= 1;
                 if (as == 0) aphase ^= 1;
             }

@@ -129,7 +129,8 @@ gemm_tc_z_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant
     const long long total = (long long)A * p.mblocks * p.nblocks;
 
     if (warp == 0) {
-        if (lane == 0) {
+        {   // the whole warp walks the ring (warp-uniform addresses); one elected lane issues the copies
+            const bool issuer = elect_one();
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -140,18 +141,21 @@ gemm_tc_z_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant
                 for (int j = 0; ok && j < A; ++j) {
                     const int xi = i * A + j;
                     for (int kc = 0; kc < p.kchunks; ++kc) {
-                        if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, TZ_WAIT_EMPTY)) { ok = false; break; }
-                        mbar_arrive_expect_tx(bar_full + 8 * stage, TC_A_BYTES + TZ_B_BYTES);
-                        tma_load_3d(a_ring + stage * TC_A_BYTES, &tm_v, bar_full + 8 * stage, kc * KC, mb * TC_BM, xi);
-                        tma_load_3d(b_ring + stage * TZ_B_BYTES, &tm_u, bar_full + 8 * stage, kc * KC, nb * TZ_BN, xi);
+                        if (!mbar_wait_warp(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, TZ_WAIT_EMPTY)) { ok = false; break; }
+                        if (issuer) {
+                            mbar_arrive_expect_tx(bar_full + 8 * stage, TC_A_BYTES + TZ_B_BYTES);
+                            tma_load_3d(a_ring + stage * TC_A_BYTES, &tm_v, bar_full + 8 * stage, kc * KC, mb * TC_BM, xi);
+                            tma_load_3d(b_ring + stage * TZ_B_BYTES, &tm_u, bar_full + 8 * stage, kc * KC, nb * TZ_BN, xi);
+                        }
                         if (++stage == STAGES) { stage = 0; phase ^= 1; }
                     }
                 }
             }
-            if (!ok) drain_after_abort();
+            if (!ok && issuer) drain_after_abort();
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        {   // warp-uniform loop, one elected lane issues: from a single-lane branch every tcgen05.mma cost its thread tens of cycles
+            const bool issuer = elect_one();
             int stage = 0;
             uint32_t phase = 0;
             unsigned long long g = 0;   // accumulators produced so far
@@ -160,22 +164,22 @@ gemm_tc_z_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant
                 for (int j = 0; ok && j < A; ++j, ++g) {
                     const int slot = (int)(g % TZ_SLOTS);
                     const uint32_t sphase = (uint32_t)((g / TZ_SLOTS) & 1);
-                    if (!mbar_wait_bounded(bar_tempty + 8 * slot, sphase ^ 1, abort_flag, p.status, TZ_WAIT_TMEM_EMPTY)) { ok = false; break; }
+                    if (!mbar_wait_warp(bar_tempty + 8 * slot, sphase ^ 1, abort_flag, p.status, TZ_WAIT_TMEM_EMPTY)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + (uint32_t)(slot * TZ_BN);
                     for (int kc = 0; kc < p.kchunks; ++kc) {
-                        if (!mbar_wait_bounded(bar_full + 8 * stage, phase, abort_flag, p.status, TZ_WAIT_FULL)) { ok = false; break; }
+                        if (!mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, p.status, TZ_WAIT_FULL)) { ok = false; break; }
                         tc_fence_after();
                         const int left = p.cp - kc * KC;
                         const int ksteps = left >= KC ? KC / UMMA_K : (left + UMMA_K - 1) / UMMA_K;
                         const uint64_t a_desc = smem_desc_k128(a_ring + stage * TC_A_BYTES), b_desc = smem_desc_k128(b_ring + stage * TZ_B_BYTES);
 #pragma unroll 4
                         for (int ks = 0; ks < ksteps; ++ks)
-                            tc_mma<TF32>(d_tmem, a_desc + (uint64_t)(ks * 2), b_desc + (uint64_t)(ks * 2), p.idesc, (kc | ks) ? 1u : 0u);
-                        tc_commit(bar_empty + 8 * stage);
+                            if (issuer) tc_mma<TF32>(d_tmem, a_desc + (uint64_t)(ks * 2), b_desc + (uint64_t)(ks * 2), p.idesc, (kc | ks) ? 1u : 0u);
+                        if (issuer) tc_commit(bar_empty + 8 * stage);
                         if (++stage == STAGES) { stage = 0; phase ^= 1; }
                     }
-                    if (ok) tc_commit(bar_tfull + 8 * slot);
+                    if (ok && issuer) tc_commit(bar_tfull + 8 * slot);
                 }
             }
         }

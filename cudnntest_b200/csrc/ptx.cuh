@@ -62,6 +62,24 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     }
 }
 
+// The same wait executed by all 32 lanes of a warp, with one verdict for the warp (so that warp-uniform code can follow).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    const bool ok = mbar_wait_bounded(bar, parity, abort_flag, status, code);
+    return __all_sync(0xffffffffu, ok);
+}
+// One lane of a fully active warp (the same lane every time it is called by that warp).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "elect.sync _|p, 0xffffffff;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // After an abort: give TMA copies that were already issued time to land before the CTA's shared memory is released.
 __device__ __forceinline__ void drain_after_abort() {
     const unsigned long long t0 = global_timer();

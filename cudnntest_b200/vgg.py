@@ -47,9 +47,9 @@ def winograd_gemm_flops_per_image(wino=4, layers=VGG16_CONV):
 
 def kernel_model(batch, dtype="bf16", wino=4, layers=VGG16_CONV, layout="NHWC", forced_wino=False):
     """Algorithmic bytes and flops of one forward pass per kernel class, following the engine's per-layer choice
-    for NHWC: C <= 3 (no pool): thin-input direct kernel; BF16 with C = 64 / 128: direct tensor-core kernel; other
-    tensor-core layers with C <= 128: row-fused tile GEMM (products Z, a*m planes, half for bf16); otherwise the
-    plain tile GEMM (products M, a*a float planes)."""
+    for NHWC: C <= 3 (no pool): thin-input direct kernel; BF16 with C a multiple of 64 and (C <= 256 or an image
+    smaller than 28 x 28): direct tensor-core kernel; other tensor-core layers with C <= 128: row-fused tile GEMM
+    (products Z, a*m planes, half for bf16); otherwise the plain tile GEMM (products M, a*a float planes)."""
     a, m = wino + 2, wino
     s_io = 2 if dtype == "bf16" else 4
     out = {k: {"bytes": 0, "flops": 0} for k in ("input_transform", "tile_gemm_plain", "tile_gemm_rowfused",
@@ -60,7 +60,7 @@ def kernel_model(batch, dtype="bf16", wino=4, layers=VGG16_CONV, layout="NHWC", 
             out["direct_thin_input"]["bytes"] += batch * (c * s * s + k * s * s) * s_io
             out["direct_thin_input"]["flops"] += batch * 2 * k * c * s * s * 9
             continue
-        if dtype == "bf16" and layout == "NHWC" and not forced_wino and c % 64 == 0 and c <= 128 and k % 8 == 0:
+        if dtype == "bf16" and layout == "NHWC" and not forced_wino and c % 64 == 0 and (c <= 256 or s * s < 28 * 28) and k % 8 == 0:
             out["direct_tensor_core"]["bytes"] += batch * (c * s * s + k * o * o) * s_io
             out["direct_tensor_core"]["flops"] += batch * 2 * k * c * s * s * 9
             continue
