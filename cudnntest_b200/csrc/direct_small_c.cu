@@ -11,8 +11,11 @@
 //     layout tcgen05.mma reads;
 //   * the 64 x 32 filter tile is built once per CTA the same way;
 //   * thread 0 issues tcgen05.mma (M = 128 pixels, N = 64 filters, K = 32) into a 64-column accumulator in tensor
-//     memory and commits to an mbarrier; every thread then reads its own accumulator lane (tcgen05.ld), adds the
-//     bias, applies ReLU and stores its pixel's 64 outputs (one contiguous 128-byte line for NHWC BF16).
+//     memory and commits to an mbarrier.  The bias is the 28th contraction slot (pixel rows hold 1, filter rows the
+//     bias rounded to the operand format), so the MMA adds it;
+//   * every thread then reads its own accumulator lane (tcgen05.ld) and applies ReLU; for dense NHWC output each
+//     warp turns its 32 pixels x 64 outputs around in shared memory so that a store instruction writes four whole
+//     128-byte lines, other layouts store element by element.
 // Several CTAs share an SM so one CTA's gather overlaps another's MMA and stores.  Bound: HBM, by the output
 // write (N*K*OH*OW elements); the input is read once from HBM and nine times from L1/L2.
 #include <cstdlib>
@@ -44,19 +47,22 @@ struct DCArgs {
 
 template <typename TIn>
 struct OperandRow;
-// BF16 storage: operands are the stored bf16 values themselves (32 x 2 bytes = four 16-byte chunks per row)
+// BF16 storage: operands are the stored bf16 values themselves, moved as raw 16-bit patterns
+// (32 x 2 bytes = four 16-byte chunks per row)
 template <>
 struct OperandRow<__nv_bfloat16> {
     static constexpr bool TF32 = false;
-    static __device__ __forceinline__ void store(uint8_t* row_base, int row, const float (&v)[32]) {
+    using raw_t = unsigned short;
+    static __device__ __forceinline__ raw_t load(const __nv_bfloat16* p) { return __ldg(reinterpret_cast<const unsigned short*>(p)); }
+    static __device__ __forceinline__ raw_t zero() { return 0; }
+    static __device__ __forceinline__ raw_t one() { return 0x3F80; }
+    static __device__ __forceinline__ raw_t from_f32(float f) { return __bfloat16_as_ushort(__float2bfloat16_rn(f)); }
+    static __device__ __forceinline__ void store(uint8_t* row_base, int row, const raw_t (&v)[32]) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             uint32_t wds[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                __nv_bfloat162 p = __floats2bfloat162_rn(v[8 * c + 2 * e], v[8 * c + 2 * e + 1]);
-                wds[e] = *reinterpret_cast<uint32_t*>(&p);
-            }
+            for (int e = 0; e < 4; ++e) wds[e] = (uint32_t)v[8 * c + 2 * e] | ((uint32_t)v[8 * c + 2 * e + 1] << 16);
             *reinterpret_cast<uint4*>(row_base + ((c ^ (row & 7)) << 4)) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
         }
     }
@@ -65,26 +71,30 @@ struct OperandRow<__nv_bfloat16> {
 template <>
 struct OperandRow<float> {
     static constexpr bool TF32 = true;
-    static __device__ __forceinline__ void store(uint8_t* row_base, int row, const float (&v)[32]) {
+    using raw_t = float;
+    static __device__ __forceinline__ raw_t load(const float* p) { return from_float<tf32_t>(__ldg(p)).v; }
+    static __device__ __forceinline__ raw_t zero() { return 0.f; }
+    static __device__ __forceinline__ raw_t one() { return 1.f; }
+    static __device__ __forceinline__ raw_t from_f32(float f) { return from_float<tf32_t>(f).v; }
+    static __device__ __forceinline__ void store(uint8_t* row_base, int row, const raw_t (&v)[32]) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            uint32_t wds[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) wds[e] = __float_as_uint(from_float<tf32_t>(v[4 * c + e]).v);
-            *reinterpret_cast<uint4*>(row_base + ((c ^ (row & 7)) << 4)) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
-        }
+        for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(row_base + ((c ^ (row & 7)) << 4)) =
+                make_uint4(__float_as_uint(v[4 * c]), __float_as_uint(v[4 * c + 1]), __float_as_uint(v[4 * c + 2]), __float_as_uint(v[4 * c + 3]));
     }
 };
 
 template <typename TIn, typename TOut, int CC>
-__global__ void __launch_bounds__(128) direct_small_c_kernel(const DCArgs a) {
+__global__ void __launch_bounds__(128, 6) direct_small_c_kernel(const DCArgs a) {
     using Row = OperandRow<TIn>;
+    using raw_t = typename Row::raw_t;
+    constexpr int BIAS_COL = 9 * CC;        // first unused contraction slot: pixel rows hold 1 there, filter rows the bias
+    static_assert(BIAS_COL < 32, "the contraction is padded to 32 and one spare slot carries the bias");
     __shared__ __align__(1024) uint8_t a_tile[128 * 128];
     __shared__ __align__(1024) uint8_t b_tile[64 * 128];
     __shared__ __align__(8) unsigned long long bar_storage;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
-    __shared__ __align__(16) float bias_s[64];
 
     const int tid = threadIdx.x, warp = tid / 32;
     const int k0 = blockIdx.y * 64;
@@ -96,19 +106,20 @@ __global__ void __launch_bounds__(128) direct_small_c_kernel(const DCArgs a) {
         mbar_fence_init();
     }
     if (warp == 0) tmem_alloc(smem_u32(&tmem_slot), 64);
-    if (tid < 64) bias_s[tid] = (a.bias && k0 + tid < a.K) ? __ldg(a.bias + k0 + tid) : 0.f;
     // dense NHWC output with a whole, 16-byte aligned block of 64 filters: pixels are consecutive 2*K-byte (4*K) rows
     const bool dense_nhwc = !a.n_fastest && a.sy.c == 1 && a.sy.w == a.K && a.sy.h == (long long)a.ow * a.K &&
                             a.sy.n == (long long)a.oh * a.ow * a.K && k0 + 64 <= a.K &&
                             ((reinterpret_cast<uintptr_t>(a.y) | (uintptr_t)(a.K * sizeof(TOut)) | (uintptr_t)(k0 * sizeof(TOut))) & 15) == 0;
 
-    // filter tile: row kf = packed filter row k0 + kf (32 operand values, see pack_direct_filters), zero beyond K
+    // filter tile: row kf = packed filter row k0 + kf (32 operand values, see pack_direct_filters), zero beyond K;
+    // the bias rides in the spare contraction slot (rounded to the operand format: it is added by the MMA itself)
     if (tid < 64) {
-        float v[32];
+        raw_t v[32];
         const int kf = k0 + tid;
         const TIn* wp = reinterpret_cast<const TIn*>(a.w) + (long long)kf * 32;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = kf < a.K ? to_float<TIn>(wp[i]) : 0.f;
+        for (int i = 0; i < 32; ++i) v[i] = kf < a.K ? Row::load(wp + i) : Row::zero();
+        v[BIAS_COL] = (a.bias && kf < a.K) ? Row::from_f32(__ldg(a.bias + kf)) : Row::zero();
         Row::store(b_tile + tid * 128, tid, v);
     }
     tc_fence_before();
@@ -121,27 +132,77 @@ __global__ void __launch_bounds__(128) direct_small_c_kernel(const DCArgs a) {
 
     uint32_t parity = 0;
     const long long tiles = (a.pixels + 127) / 128;
+    const bool idx32 = a.pixels < (1LL << 31);
+    // dense NHWC input with exactly three channels, 4-byte aligned
+    const bool nhwc3_in = !a.n_fastest && a.C == 3 && a.sx.c == 1 && a.sx.w == 3 && a.sx.h == 3LL * a.W && a.sx.n == 3LL * a.W * a.H &&
+                          (reinterpret_cast<uintptr_t>(a.x) & 3) == 0 && a.W >= 4 && a.pad <= 1;
     for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
         const long long p = tile * 128 + tid;
         const bool valid = p < a.pixels;
         int n = 0, oy = 0, ox = 0;
         if (valid) {
-            if (a.n_fastest) {          // CHWN: consecutive threads take consecutive images of one output position
-                n = (int)(p % a.N);
-                const long long q = p / a.N;
-                ox = (int)(q % a.ow);
-                oy = (int)(q / a.ow);
+            // pixel index -> (image, row, column): 32-bit arithmetic whenever the tensor allows it
+            const int inner = a.n_fastest ? a.N : a.ow, mid = a.n_fastest ? a.ow : a.oh;
+            int i0, i1, i2;
+            if (idx32) {
+                const unsigned q = (unsigned)p, q1 = q / (unsigned)inner;
+                i0 = (int)(q - q1 * (unsigned)inner);
+                i2 = (int)(q1 / (unsigned)mid);
+                i1 = (int)(q1 - (unsigned)i2 * (unsigned)mid);
             } else {
-                ox = (int)(p % a.ow);
-                const long long q = p / a.ow;
-                oy = (int)(q % a.oh);
-                n = (int)(q / a.oh);
+                i0 = (int)(p % inner);
+                const long long q1 = p / inner;
+                i1 = (int)(q1 % mid);
+                i2 = (int)(q1 / mid);
+            }
+            if (a.n_fastest) { n = i0; ox = i1; oy = i2; }     // CHWN: consecutive threads take consecutive images of one output position
+            else { ox = i0; oy = i1; n = i2; }
+        }
+        bool fast = false;
+        if constexpr (sizeof(TIn) == 2 && CC == 3) {
+            // Dense NHWC input with exactly three channels: the nine taps of a filter row are 18 contiguous bytes.
+            // Interior pixels fetch them as five aligned 32-bit words per row and shift them into place (the start
+            // is only 2-byte aligned); pixels on the left / right image border take the element-wise gather below.
+            // (the aligned words of a row may include the element after its ninth tap: not for the tensor's very last row)
+            fast = valid && nhwc3_in && ox >= a.pad && ox + 2 - a.pad < a.W &&
+                   !(n == a.N - 1 && oy + 2 - a.pad >= a.H - 1 && ox + 3 - a.pad >= a.W);
+            if (fast) {
+                const long long m_pix = ((long long)n * a.H * a.W + (ox - a.pad)) * 3;       // element offset of tap (row 0 of the image, s = 0)
+                uint32_t st[3][5];
+#pragma unroll
+                for (int r = 0; r < 3; ++r) {
+                    const int ih = oy + r - a.pad;
+                    const bool row_ok = ih >= 0 && ih < a.H;
+                    const long long m0 = m_pix + (long long)(row_ok ? ih : 0) * a.W * 3;
+                    const uint32_t* wp = reinterpret_cast<const uint32_t*>(xin) + (m0 >> 1);
+                    const uint32_t sh = (uint32_t)(m0 & 1) * 16;
+                    uint32_t aw[5];
+#pragma unroll
+                    for (int k = 0; k < 5; ++k) aw[k] = row_ok ? __ldg(wp + k) : 0u;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) st[r][k] = __funnelshift_r(aw[k], aw[k + 1], sh);
+                    st[r][4] = aw[4] >> sh;
+                }
+                // operand row: elements 0..8 = filter row 0, 9..17 = row 1, 18..26 = row 2, 27 = 1 (bias slot), 28..31 = 0
+                uint32_t w[16];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) w[k] = st[0][k];
+                w[4] = (st[0][4] & 0xFFFFu) | (st[1][0] << 16);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) w[5 + k] = __funnelshift_r(st[1][k], st[1][k + 1], 16);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) w[9 + k] = st[2][k];
+                w[13] = (st[2][4] & 0xFFFFu) | ((uint32_t)Row::one() << 16);
+                w[14] = 0u; w[15] = 0u;
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    *reinterpret_cast<uint4*>(a_tile + tid * 128 + ((c ^ (tid & 7)) << 4)) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
             }
         }
-        {
-            float v[32];
+        if (!fast) {
+            raw_t v[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            for (int i = 0; i < 32; ++i) v[i] = Row::zero();
             if (valid) {
                 const TIn* xp = xin + n * a.sx.n;
 #pragma unroll
@@ -154,9 +215,10 @@ __global__ void __launch_bounds__(128) direct_small_c_kernel(const DCArgs a) {
                         if (iw < 0 || iw >= a.W) continue;
 #pragma unroll
                         for (int c = 0; c < CC; ++c)
-                            if (c < a.C) v[(r * 3 + s) * CC + c] = to_float<TIn>(xp[c * a.sx.c + ih * a.sx.h + iw * a.sx.w]);
+                            if (c < a.C) v[(r * 3 + s) * CC + c] = Row::load(xp + c * a.sx.c + ih * a.sx.h + iw * a.sx.w);
                     }
                 }
+                v[BIAS_COL] = Row::one();
             }
             Row::store(a_tile + tid * 128, tid, v);
         }
@@ -194,29 +256,23 @@ __global__ void __launch_bounds__(128) direct_small_c_kernel(const DCArgs a) {
             for (int pass = 0; pass < PASSES; ++pass) {
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    float o[PER];
-                    const float4* bp = reinterpret_cast<const float4*>(bias_s + pass * 8 * PER + c * PER);
-#pragma unroll
-                    for (int q = 0; q < PER / 4; ++q) {
-                        const float4 b4 = bp[q];
-                        const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int kk = pass * 8 * PER + c * PER + q * 4 + e;
-                            const float val = __uint_as_float(kk < 32 ? r0[kk] : r1[kk - 32]) + bb[e];
-                            o[q * 4 + e] = a.relu ? fmaxf(val, 0.f) : val;
-                        }
-                    }
                     uint32_t wds[4];
                     if constexpr (sizeof(TOut) == 2) {
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            __nv_bfloat162 h = __floats2bfloat162_rn(o[2 * e], o[2 * e + 1]);
+                            const int kk = c * 8 + 2 * e;         // one pass: 64 filters
+                            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(kk < 32 ? r0[kk] : r1[kk - 32]),
+                                                                     __uint_as_float(kk + 1 < 32 ? r0[kk + 1] : r1[kk + 1 - 32]));
+                            if (a.relu) h = __hmax2(h, __floats2bfloat162_rn(0.f, 0.f));   // ReLU commutes with the rounding
                             wds[e] = *reinterpret_cast<uint32_t*>(&h);
                         }
                     } else {
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) wds[e] = __float_as_uint(o[e]);
+                        for (int e = 0; e < 4; ++e) {
+                            const int kk = pass * 32 + c * 4 + e;
+                            const float val = __uint_as_float(kk < 32 ? r0[kk] : r1[kk - 32]);
+                            wds[e] = __float_as_uint(a.relu ? fmaxf(val, 0.f) : val);
+                        }
                     }
                     *reinterpret_cast<uint4*>(wtile + lane * 128 + ((c ^ (lane & 7)) << 4)) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
                 }
@@ -231,40 +287,14 @@ __global__ void __launch_bounds__(128) direct_small_c_kernel(const DCArgs a) {
                 __syncwarp();
             }
         } else if (valid) {
+            // any other output layout, or a ragged block of filters: one element at a time
             TOut* yp = yout + n * a.sy.n + oy * a.sy.h + ox * a.sy.w;
-            if (a.sy.c == 1 && k0 + 64 <= a.K && (reinterpret_cast<uintptr_t>(yp + k0) & 15) == 0) {
-                // filters contiguous (NHWC): 16-byte stores
-                constexpr int PER = 16 / (int)sizeof(TOut);
 #pragma unroll
-                for (int c = 0; c < 64 / PER; ++c) {
-                    float o[PER];
-#pragma unroll
-                    for (int e = 0; e < PER; ++e) {
-                        const int kk = c * PER + e;
-                        const float val = __uint_as_float(kk < 32 ? r0[kk] : r1[kk - 32]) + (a.bias ? __ldg(a.bias + k0 + kk) : 0.f);
-                        o[e] = a.relu ? fmaxf(val, 0.f) : val;
-                    }
-                    uint32_t wds[4];
-                    if constexpr (sizeof(TOut) == 2) {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            __nv_bfloat162 h = __floats2bfloat162_rn(o[2 * e], o[2 * e + 1]);
-                            wds[e] = *reinterpret_cast<uint32_t*>(&h);
-                        }
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) wds[e] = __float_as_uint(o[e]);
-                    }
-                    *reinterpret_cast<uint4*>(yp + k0 + c * PER) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
-                }
-            } else {
-#pragma unroll
-                for (int kk = 0; kk < 64; ++kk) {
-                    if (k0 + kk >= a.K) break;
-                    float val = __uint_as_float(kk < 32 ? r0[kk] : r1[kk - 32]) + (a.bias ? __ldg(a.bias + k0 + kk) : 0.f);
-                    if (a.relu) val = fmaxf(val, 0.f);
-                    yp[(long long)(k0 + kk) * a.sy.c] = from_float<TOut>(val);
-                }
+            for (int kk = 0; kk < 64; ++kk) {
+                if (k0 + kk >= a.K) break;
+                float val = __uint_as_float(kk < 32 ? r0[kk] : r1[kk - 32]);
+                if (a.relu) val = fmaxf(val, 0.f);
+                yp[(long long)(k0 + kk) * a.sy.c] = from_float<TOut>(val);
             }
         }
     }
