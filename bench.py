@@ -38,6 +38,7 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=256, help="images per GPU per step")
     ap.add_argument("--wino", type=int, default=0, choices=[0, 2, 4])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     ap.add_argument("--gather", action="store_true", help="after the timed region, all-gather the final outputs over NCCL once")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the cpu_baseline sample")
     return ap.parse_args()
@@ -177,7 +178,8 @@ def workload_config(args):
             "per_gpu_batch": args.batch, "global_batch": args.batch * args.gpus, "layout": args.layout,
             "parallelism": "batch-sharded x%d, no collective" % args.gpus,
             "init": "He-normal weights, bias N(0,0.01), input U[-1,1], seeded",
-            "l2": "256 MiB buffer rewritten between timed iterations"}
+            "l2": "256 MiB buffer rewritten between timed iterations",
+            "launch": "host launches" if getattr(args, "no_graph", False) else "one CUDA graph replay per step"}
 
 
 # ---- GPU arm --------------------------------------------------------------------------------------------
@@ -226,13 +228,30 @@ def run_ours(args, rank, world, local_rank):
             ms = float(t.item())
         return ms
 
+    # The forward pass is replayed from a CUDA graph (one per input buffer) unless --no-graph is given.
+    x_bufs = [torch.empty_like(x_dev), torch.empty_like(x_dev)]
+    graphs = None
+    if not args.no_graph:
+        graphs = [stack.capture(b) for b in [x_dev] + x_bufs]
+    launch_counter = {"n": 0}
+
+    def run_stack(which):
+        """which: 0 = resident input, 1 / 2 = the end-to-end input buffers.  Returns the output view."""
+        if graphs is None:
+            before = L.wino_launch_count()
+            y = stack(([x_dev] + x_bufs)[which])
+            launch_counter["n"] += L.wino_launch_count() - before
+            return y
+        graphs[which][0].replay()
+        launch_counter["n"] += stack.launches_per_forward
+        return graphs[which][1]
+
     def step_resident():
-        stack(x_dev)
+        run_stack(0)
 
     # End-to-end step: every step copies ITS input batch from pinned host memory and its result back.  The copy of
     # step i+1's input runs on a second stream into the other of two device buffers while step i computes.
     copy_stream = torch.cuda.Stream()
-    x_bufs = [torch.empty_like(x_dev), torch.empty_like(x_dev)]
     ready = [torch.cuda.Event(), torch.cuda.Event()]       # input buffer b holds the next batch
     freed = [torch.cuda.Event(), torch.cuda.Event()]       # the compute that read buffer b has been issued and finished
     e2e_state = {"i": 0, "primed": False}
@@ -251,7 +270,7 @@ def run_ours(args, rank, world, local_rank):
             e2e_state["primed"] = True
         upload(b ^ 1)                      # next step's input, overlapped with this step's compute
         stream.wait_event(ready[b])
-        y = stack(x_bufs[b])
+        y = run_stack(1 + b)
         freed[b].record(stream)
         y_host.copy_(y, non_blocking=True)
         e2e_state["i"] += 1
@@ -262,9 +281,9 @@ def run_ours(args, rank, world, local_rank):
     for _ in range(max(args.warmup, 3)):
         step_resident()
     cb.device_status()
-    launches0 = L.wino_launch_count()
+    launch_counter["n"] = 0
     ms = timed(step_resident, args.steps)
-    launches = L.wino_launch_count() - launches0
+    launches = launch_counter["n"]
     clocks = sampler.stop() if rank == 0 else None
     cb.device_status()
 
@@ -276,7 +295,7 @@ def run_ours(args, rank, world, local_rank):
     # per-stage device time of one more step, each kernel bracketed by events on its stream
     import ctypes
     L.wino_profile_enable(1)
-    step_resident()
+    stack(x_dev)                   # launched from the host: the profiling events are not part of the captured graph
     stage_ms = (ctypes.c_float * 8)()
     stage_n = (ctypes.c_longlong * 8)()
     L.wino_profile_read(stage_ms, stage_n)
