@@ -245,13 +245,14 @@ size_t wino_filter_bytes(const wino_conv_desc* d) {
     // thin-input layers keep packed raw filters instead (always smaller); report the larger so either path fits
     size_t need = wino;
     if (direct_small_c_applies(*d) && direct_small_c_filter_bytes(*d) > need) need = direct_small_c_filter_bytes(*d);
-    if (direct_tc_applies(*d) && direct_tc_filter_bytes(*d) > need) need = direct_tc_filter_bytes(*d);
+    if ((direct_tc_applies(*d) || direct_via_nhwc_applies(*d)) && direct_tc_filter_bytes(*d) > need) need = direct_tc_filter_bytes(*d);
     return need;
 }
 
 size_t wino_conv_workspace_bytes(const wino_conv_desc* d) {
     Geometry g;
     if (make_geometry(d, &g) != WINO_OK) return 0;
+    if (direct_via_nhwc_applies(*d)) return direct_via_nhwc_staging_bytes(*d, g);
     const long long tp = tile_rows(g, slab_images(*d, g));
     return v_bytes(g, tp) + prod_bytes(g, tp) + 1024;
 }
@@ -281,7 +282,7 @@ int wino_filter_transform(const wino_conv_desc* d, const void* w, void* u, wino_
     if (!w || !u) return fail(WINO_E_BADARG, "filter transform: NULL pointer");
     if ((rc = check_device())) return rc;
     if (direct_small_c_applies(*d)) return launch_direct_small_c_pack(*d, w, u, (cudaStream_t)stream);
-    if (direct_tc_applies(*d)) return launch_direct_tc_pack(*d, w, u, (cudaStream_t)stream);
+    if (direct_tc_applies(*d) || direct_via_nhwc_applies(*d)) return launch_direct_tc_pack(*d, w, u, (cudaStream_t)stream);
     return launch_filter_transform(*d, g, w, u, (cudaStream_t)stream);
 }
 
@@ -352,6 +353,7 @@ int wino_conv_forward(const wino_conv_desc* d, const void* x, const void* u, con
     if ((rc = check_device())) return rc;
     if (direct_small_c_applies(*d)) return launch_direct_small_c(*d, g, x, u, bias, y, (cudaStream_t)stream);
     if (direct_tc_applies(*d)) return launch_direct_tc(*d, g, x, u, bias, y, (cudaStream_t)stream);
+    if (direct_via_nhwc_applies(*d)) return launch_direct_via_nhwc(*d, g, x, u, bias, y, workspace, workspace_bytes, (cudaStream_t)stream);
     const int ns = slab_images(*d, g);
     const long long tp = tile_rows(g, ns);
     const size_t need = v_bytes(g, tp) + prod_bytes(g, tp) + 1024;

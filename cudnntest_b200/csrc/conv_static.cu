@@ -68,6 +68,16 @@ int wino_conv_forward_static(const wino_conv_desc* d, const void* x, const void*
     if ((rc = check_device())) return rc;
     if (direct_small_c_applies(*d)) return launch_direct_small_c(*d, g, x, u, bias, y, (cudaStream_t)stream);   // needs no scratch
     if (direct_tc_applies(*d)) return launch_direct_tc(*d, g, x, u, bias, y, (cudaStream_t)stream);               // needs no scratch
+    if (direct_via_nhwc_applies(*d)) {      // NHWC staging of the whole batch has to fit the array
+        const size_t need = direct_via_nhwc_staging_bytes(*d, g);
+        if (need > kStaticScratchBytes)
+            return fail(WINO_E_WORKSPACE,
+                        "conv forward (static scratch): the NHWC staging of this layer needs %zu bytes, the built-in array holds %zu; "
+                        "use wino_conv_forward with caller-provided scratch for this size", need, kStaticScratchBytes);
+        void* staging = nullptr;
+        if ((rc = static_scratch(&staging))) return rc;
+        return launch_direct_via_nhwc(*d, g, x, u, bias, y, staging, kStaticScratchBytes, (cudaStream_t)stream);
+    }
 
     // largest slab whose V + M (with the same 1 KiB carving as wino_conv_forward) fits the array
     const size_t one = v_bytes(g, tile_rows(g, 1)) + prod_bytes(g, tile_rows(g, 1)) + 1024;

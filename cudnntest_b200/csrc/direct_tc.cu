@@ -308,6 +308,49 @@ bool direct_tc_applies(const wino_conv_desc& d) {
 
 size_t direct_tc_filter_bytes(const wino_conv_desc& d) { return (size_t)9 * d.k * d.c * 2; }
 
+static wino_conv_desc nhwc_twin(const wino_conv_desc& d) {
+    wino_conv_desc t = d;
+    t.layout_in = WINO_NHWC; t.layout_out = WINO_NHWC;
+    return t;
+}
+
+bool direct_via_nhwc_applies(const wino_conv_desc& d) {
+    static const bool off = [] { const char* e = getenv("WINO_DIRECT_RELAYOUT"); return e && e[0] == '0'; }();
+    if (off || (d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC)) return false;
+    return direct_tc_applies(nhwc_twin(d));
+}
+
+static size_t round1k(size_t v) { return (v + 1023) & ~(size_t)1023; }
+
+size_t direct_via_nhwc_staging_bytes(const wino_conv_desc& d, const Geometry& g) {
+    size_t need = 1024;
+    if (d.layout_in != WINO_NHWC) need += round1k((size_t)d.n * d.c * d.h * d.w * 2);
+    if (d.layout_out != WINO_NHWC) need += round1k((size_t)d.n * d.k * g.ph * g.pw * 2);
+    return need;
+}
+
+int launch_direct_via_nhwc(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,
+                           void* scratch, size_t scratch_bytes, cudaStream_t st) {
+    const size_t need = direct_via_nhwc_staging_bytes(d, g);
+    if (!scratch || scratch_bytes < need)
+        return fail(WINO_E_WORKSPACE, "conv forward: workspace of %zu bytes given, %zu needed (NHWC staging)", scratch_bytes, need);
+    uintptr_t p = ((uintptr_t)scratch + 1023) & ~(uintptr_t)1023;
+    const void* xin = x;
+    void* yout = y;
+    int rc;
+    if (d.layout_in != WINO_NHWC) {
+        void* xs = (void*)p;
+        p += round1k((size_t)d.n * d.c * d.h * d.w * 2);
+        if ((rc = launch_relayout(d.layout_in, WINO_NHWC, d.n, d.c, d.h, d.w, 2, x, xs, st))) return rc;
+        xin = xs;
+    }
+    if (d.layout_out != WINO_NHWC) yout = (void*)p;
+    const wino_conv_desc t = nhwc_twin(d);
+    if ((rc = launch_direct_tc(t, g, xin, packed, bias, yout, st))) return rc;
+    if (d.layout_out != WINO_NHWC) return launch_relayout(WINO_NHWC, d.layout_out, d.n, d.k, g.ph, g.pw, 2, yout, y, st);
+    return WINO_OK;
+}
+
 int launch_direct_tc_pack(const wino_conv_desc& d, const void* w, void* packed, cudaStream_t st) {
     const long long total = (long long)9 * d.k * d.c;
     ProfScope prof(STAGE_FILTER, st);
