@@ -231,7 +231,7 @@ direct_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                     }
                 }
                 if (writer) {
-                    __nv_bfloat16* dst = p.y + pix * p.K + k0;
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.y) + pix * p.K + k0;
                     if (k0 + 32 <= p.K && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
                         for (int c = 0; c < 4; ++c) reinterpret_cast<uint4*>(dst)[c] = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
@@ -257,14 +257,16 @@ direct_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 }
 
 // Filters for the kernel above: Wd[tap = 3r + s][k][Cp] = w[k][c][r][s] (any filter layout in, bf16), zero beyond C
-__global__ void pack_direct_tc_filters(const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, int K, int C, int Cp,
-                                       Strides sw) {
+template <typename T>
+__global__ void pack_direct_tc_filters(const T* __restrict__ w, T* __restrict__ out, int K, int C, int Cp, Strides sw) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long long)9 * K * Cp) return;
     const int c = (int)(idx % Cp);
     const int k = (int)((idx / Cp) % K);
     const int tap = (int)(idx / ((long long)Cp * K));
-    out[idx] = c < C ? w[k * sw.n + c * sw.c + (tap / 3) * sw.h + (tap % 3) * sw.w] : __float2bfloat16(0.f);
+    float v = c < C ? to_float<T>(w[k * sw.n + c * sw.c + (tap / 3) * sw.h + (tap % 3) * sw.w]) : 0.f;
+    if (sizeof(T) == 4) v = from_float<tf32_t>(v).v;       // float filters are rounded to TF32 once, here
+    out[idx] = from_float<T>(v);
 }
 
 template <int BN, int A_STAGES, int B_STAGES, bool B_RESIDENT>
@@ -300,13 +302,19 @@ bool direct_tc_applies(const wino_conv_desc& d) {
     // buffers are HBM-bound); at 512 channels Winograd's 4x fewer multiplies win, except on small images
     // (14 x 14) where its tile GEMMs are too small to fill the machine.
     static const int max_c = [] { const char* e = getenv("WINO_DIRECT_TC_MAXC"); return e ? atoi(e) : -1; }();
-    if (!(d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC && d.dtype == WINO_BF16 && d.c % 64 == 0 && d.k % 8 == 0 && d.wino == 0))
-        return false;
+    if (!(d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC && d.wino == 0)) return false;
+    if (d.dtype == WINO_TF32) {
+        // float storage, TF32 operands: CTA-pair kernel only (32 channels per 128-byte chunk).  At half the tensor rate
+        // of BF16 the direct kernel stays ahead of the Winograd pipeline up to 256 channels.
+        if (!(d.c % 32 == 0 && direct_tc2_applies(d))) return false;
+        return max_c >= 0 ? d.c <= max_c : d.c <= 256;
+    }
+    if (!(d.dtype == WINO_BF16 && d.c % 64 == 0 && d.k % 8 == 0)) return false;
     if (max_c >= 0) return d.c <= max_c;
     return d.c <= 256 || (long long)d.h * d.w < 28 * 28;
 }
 
-size_t direct_tc_filter_bytes(const wino_conv_desc& d) { return (size_t)9 * d.k * d.c * 2; }
+size_t direct_tc_filter_bytes(const wino_conv_desc& d) { return (size_t)9 * d.k * d.c * (d.dtype == WINO_BF16 ? 2 : 4); }
 
 static wino_conv_desc nhwc_twin(const wino_conv_desc& d) {
     wino_conv_desc t = d;
@@ -323,9 +331,10 @@ bool direct_via_nhwc_applies(const wino_conv_desc& d) {
 static size_t round1k(size_t v) { return (v + 1023) & ~(size_t)1023; }
 
 size_t direct_via_nhwc_staging_bytes(const wino_conv_desc& d, const Geometry& g) {
+    const size_t es = d.dtype == WINO_BF16 ? 2 : 4;
     size_t need = 1024;
-    if (d.layout_in != WINO_NHWC) need += round1k((size_t)d.n * d.c * d.h * d.w * 2);
-    if (d.layout_out != WINO_NHWC) need += round1k((size_t)d.n * d.k * g.ph * g.pw * 2);
+    if (d.layout_in != WINO_NHWC) need += round1k((size_t)d.n * d.c * d.h * d.w * es);
+    if (d.layout_out != WINO_NHWC) need += round1k((size_t)d.n * d.k * g.ph * g.pw * es);
     return need;
 }
 
@@ -334,20 +343,21 @@ int launch_direct_via_nhwc(const wino_conv_desc& d, const Geometry& g, const voi
     const size_t need = direct_via_nhwc_staging_bytes(d, g);
     if (!scratch || scratch_bytes < need)
         return fail(WINO_E_WORKSPACE, "conv forward: workspace of %zu bytes given, %zu needed (NHWC staging)", scratch_bytes, need);
+    const int es = d.dtype == WINO_BF16 ? 2 : 4;
     uintptr_t p = ((uintptr_t)scratch + 1023) & ~(uintptr_t)1023;
     const void* xin = x;
     void* yout = y;
     int rc;
     if (d.layout_in != WINO_NHWC) {
         void* xs = (void*)p;
-        p += round1k((size_t)d.n * d.c * d.h * d.w * 2);
-        if ((rc = launch_relayout(d.layout_in, WINO_NHWC, d.n, d.c, d.h, d.w, 2, x, xs, st))) return rc;
+        p += round1k((size_t)d.n * d.c * d.h * d.w * es);
+        if ((rc = launch_relayout(d.layout_in, WINO_NHWC, d.n, d.c, d.h, d.w, es, x, xs, st))) return rc;
         xin = xs;
     }
     if (d.layout_out != WINO_NHWC) yout = (void*)p;
     const wino_conv_desc t = nhwc_twin(d);
     if ((rc = launch_direct_tc(t, g, xin, packed, bias, yout, st))) return rc;
-    if (d.layout_out != WINO_NHWC) return launch_relayout(WINO_NHWC, d.layout_out, d.n, d.k, g.ph, g.pw, 2, yout, y, st);
+    if (d.layout_out != WINO_NHWC) return launch_relayout(WINO_NHWC, d.layout_out, d.n, d.k, g.ph, g.pw, es, yout, y, st);
     return WINO_OK;
 }
 
@@ -355,8 +365,12 @@ int launch_direct_tc_pack(const wino_conv_desc& d, const void* w, void* packed, 
     const long long total = (long long)9 * d.k * d.c;
     ProfScope prof(STAGE_FILTER, st);
     count_launch();
-    pack_direct_tc_filters<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)packed, d.k, d.c, d.c,
-                                                                          filter_strides(d.layout_in, d.k, d.c));
+    if (d.dtype == WINO_TF32)
+        pack_direct_tc_filters<float><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const float*)w, (float*)packed, d.k, d.c, d.c,
+                                                                                     filter_strides(d.layout_in, d.k, d.c));
+    else
+        pack_direct_tc_filters<__nv_bfloat16><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+            (const __nv_bfloat16*)w, (__nv_bfloat16*)packed, d.k, d.c, d.c, filter_strides(d.layout_in, d.k, d.c));
     WINO_CUDA_CHECK(cudaGetLastError());
     return WINO_OK;
 }
@@ -368,7 +382,7 @@ int launch_direct_tc(const wino_conv_desc& d, const Geometry& g, const void* x, 
     if (((uintptr_t)x | (uintptr_t)packed | (uintptr_t)y | (d.has_bias ? (uintptr_t)bias : 0)) & 15)
         return fail(WINO_E_BADARG, "direct conv: buffers (and the bias) must be 16-byte aligned");
     DtParams p;
-    p.bias = d.has_bias ? bias : nullptr; p.y = (__nv_bfloat16*)y;
+    p.bias = d.has_bias ? bias : nullptr; p.y = y;
     p.N = d.n; p.OH = g.oh; p.OW = g.ow; p.K = d.k; p.pad = d.pad; p.PH = g.ph; p.PW = g.pw;
     p.tiles_x = (g.ow + DT_TW - 1) / DT_TW; p.tiles_y = (g.oh + DT_TH - 1) / DT_TH;
     p.cchunks = d.c / 64;

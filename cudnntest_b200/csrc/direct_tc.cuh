@@ -17,7 +17,7 @@ enum DtWaitCode { DT_W_A_EMPTY = 41, DT_W_A_FULL = 42, DT_W_B_EMPTY = 43, DT_W_B
 
 struct DtParams {
     const float* bias;
-    __nv_bfloat16* y;
+    void* y;                     // bfloat16 (BF16 variant) or float (TF32 variant)
     int N, OH, OW, K, pad;
     int PH, PW;                  // stored output size (after the optional pool)
     int tiles_x, tiles_y, nblocks, cchunks;

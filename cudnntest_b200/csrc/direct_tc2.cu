@@ -42,12 +42,13 @@ struct Dt2Smem {
     static constexpr int TOTAL = SLOT_OFF + 16 + 1024;
 };
 
-template <int BN, int MT, int A_STAGES, int B_STAGES, bool B_RESIDENT, int RES_CHUNKS>
+template <int BN, int MT, int A_STAGES, int B_STAGES, bool B_RESIDENT, int RES_CHUNKS, bool TF32>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(DT_THREADS, 1)
 direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const DtParams p) {
     using L = Dt2Smem<BN, MT, A_STAGES, B_STAGES, B_RESIDENT, RES_CHUNKS>;
     static_assert(L::ACC >= 2, "accumulators are at least double-buffered");
     constexpr int ACC = L::ACC;
+    constexpr int CPC = TF32 ? 32 : 64;      // channels per 128-byte chunk
     static_assert(A_STAGES >= MT, "one work item needs MT boxes in flight");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;      // same offset in both CTAs of the pair
@@ -107,7 +108,7 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 const uint32_t bres_leader = mapa_shared(bar_bres, 0);
                 for (int ch = 0; ch < p.cchunks; ++ch)
                     for (int tap = 0; tap < 9; ++tap)
-                        if (issuer) tma_load_3d_pair(base + L::B_OFF + (ch * 9 + tap) * L::B_TILE, &tm_w, bres_leader, ch * 64,
+                        if (issuer) tma_load_3d_pair(base + L::B_OFF + (ch * 9 + tap) * L::B_TILE, &tm_w, bres_leader, ch * CPC,
                                          my_nb * BN + filter_row0, tap);
             }
             unsigned long long acount = 0, bcount = 0;
@@ -120,7 +121,7 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         const int st = (int)(acount % A_STAGES);
                         if (!mbar_wait_warp(bar_aempty + 8 * st, (uint32_t)(((acount / A_STAGES) & 1) ^ 1), abort_flag, p.status, DT_W_A_EMPTY)) { ok = false; break; }
                         if (rank == 0 && issuer) mbar_arrive_expect_tx(bar_afull + 8 * st, 2 * DT_A_BYTES);
-                        if (issuer) tma_load_4d_pair(base + L::A_OFF + st * DT_A_STRIDE, &tm_x, mapa_shared(bar_afull + 8 * st, 0), ch * 64,
+                        if (issuer) tma_load_4d_pair(base + L::A_OFF + st * DT_A_STRIDE, &tm_x, mapa_shared(bar_afull + 8 * st, 0), ch * CPC,
                                          tx * DT_TW - p.pad, ty * DT_TH - p.pad, n);
                         ++acount;
                     }
@@ -130,7 +131,7 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                             const int sb = (int)(bcount % B_STAGES);
                             if (!mbar_wait_warp(bar_bempty + 8 * sb, (uint32_t)(((bcount / B_STAGES) & 1) ^ 1), abort_flag, p.status, DT_W_B_EMPTY)) { ok = false; break; }
                             if (rank == 0 && issuer) mbar_arrive_expect_tx(bar_bfull + 8 * sb, 2 * L::B_TILE);
-                            if (issuer) tma_load_3d_pair(base + L::B_OFF + sb * L::B_TILE, &tm_w, mapa_shared(bar_bfull + 8 * sb, 0), ch * 64,
+                            if (issuer) tma_load_3d_pair(base + L::B_OFF + sb * L::B_TILE, &tm_w, mapa_shared(bar_bfull + 8 * sb, 0), ch * CPC,
                                              nb * BN + filter_row0, tap);
                             ++bcount;
                         }
@@ -183,9 +184,9 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 #pragma unroll
                             for (int ks = 0; ks < 4; ++ks) {
                                 if (tap == 0 && ks == 0)
-                                    { if (issuer) tc_mma_pair_f16(d_tmem + mt * BN, a_desc, b_desc0, p.idesc, ch ? 1u : 0u); }
+                                    { if (issuer) tc_mma_pair<TF32>(d_tmem + mt * BN, a_desc, b_desc0, p.idesc, ch ? 1u : 0u); }
                                 else
-                                    { if (issuer) tc_mma_pair_f16(d_tmem + mt * BN, a_desc + (uint64_t)(ks * 2), b_desc0 + (uint64_t)(ks * 2), p.idesc, 1u); }
+                                    { if (issuer) tc_mma_pair<TF32>(d_tmem + mt * BN, a_desc + (uint64_t)(ks * 2), b_desc0 + (uint64_t)(ks * 2), p.idesc, 1u); }
                             }
                         }
                         if (!B_RESIDENT) { if (issuer) tc_commit_pair(bar_bempty + 8 * sb, 3); ++bcount; }
@@ -240,6 +241,39 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * as);
                     }
                     const int k0 = nb * BN + half * (BN / 2) + chunk * 32;
+                    if constexpr (TF32) {
+                        // float storage: bias + ReLU, the 2x2 max with two shuffles per value, 16-byte stores
+                        float v[32];
+#pragma unroll
+                        for (int e = 0; e < 32; e += 4) {
+                            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (p.bias && k0 + e + 4 <= p.K) b4 = __ldg(reinterpret_cast<const float4*>(p.bias + k0 + e));
+                            v[e] = __uint_as_float(r[e]) + b4.x; v[e + 1] = __uint_as_float(r[e + 1]) + b4.y;
+                            v[e + 2] = __uint_as_float(r[e + 2]) + b4.z; v[e + 3] = __uint_as_float(r[e + 3]) + b4.w;
+                        }
+                        if (p.relu) {
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) v[e] = fmaxf(v[e], 0.f);
+                        }
+                        if (p.pool) {
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) {
+                                v[e] = fmaxf(v[e], __shfl_xor_sync(0xffffffffu, v[e], 1));
+                                v[e] = fmaxf(v[e], __shfl_xor_sync(0xffffffffu, v[e], 8));
+                            }
+                        }
+                        if (writer) {
+                            float* dst = reinterpret_cast<float*>(p.y) + pix * p.K + k0;
+                            if (k0 + 32 <= p.K && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                                for (int c = 0; c < 8; ++c) reinterpret_cast<float4*>(dst)[c] = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 32; ++e)
+                                    if (k0 + e < p.K) dst[e] = v[e];
+                            }
+                        }
+                    } else {
                     // bias + ReLU, packed to bf16 pairs; the 2x2 max is taken on the packed values (rounding is monotonic)
                     uint32_t w[16];
 #pragma unroll
@@ -265,7 +299,7 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         }
                     }
                     if (writer) {
-                        __nv_bfloat16* dst = p.y + pix * p.K + k0;
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.y) + pix * p.K + k0;
                         if (k0 + 32 <= p.K && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
                             for (int c = 0; c < 4; ++c) reinterpret_cast<uint4*>(dst)[c] = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
@@ -274,6 +308,7 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                             for (int e = 0; e < 32; ++e)
                                 if (k0 + e < p.K) dst[e] = reinterpret_cast<const __nv_bfloat16*>(w)[e];
                         }
+                    }
                     }
                 }
             }
@@ -291,7 +326,7 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     }
 }
 
-template <int BN, int MT, int A_STAGES, int B_STAGES, bool B_RESIDENT, int RES_CHUNKS>
+template <int BN, int MT, int A_STAGES, int B_STAGES, bool B_RESIDENT, int RES_CHUNKS, bool TF32>
 int run2(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const DtParams& p, cudaStream_t st) {
     using L = Dt2Smem<BN, MT, A_STAGES, B_STAGES, B_RESIDENT, RES_CHUNKS>;
     static_assert(L::TOTAL <= 232448, "shared memory budget of one CTA exceeded");
@@ -300,7 +335,7 @@ int run2(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const DtParams& p, cu
     WINO_CUDA_CHECK(cudaGetDevice(&dev));
     cudaError_t attr_err = cudaSuccess;
     std::call_once(once[dev & 63], [&] {
-        attr_err = cudaFuncSetAttribute(direct_tc2_kernel<BN, MT, A_STAGES, B_STAGES, B_RESIDENT, RES_CHUNKS>,
+        attr_err = cudaFuncSetAttribute(direct_tc2_kernel<BN, MT, A_STAGES, B_STAGES, B_RESIDENT, RES_CHUNKS, TF32>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     });
     WINO_CUDA_CHECK(attr_err);
@@ -312,7 +347,7 @@ int run2(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const DtParams& p, cu
     if (pairs < 1) pairs = p.nblocks;
     ProfScope prof(STAGE_DIRECT_TC, st);
     count_launch();
-    direct_tc2_kernel<BN, MT, A_STAGES, B_STAGES, B_RESIDENT, RES_CHUNKS><<<(unsigned)(2 * pairs), DT_THREADS, L::TOTAL, st>>>(tm_x, tm_w, p);
+    direct_tc2_kernel<BN, MT, A_STAGES, B_STAGES, B_RESIDENT, RES_CHUNKS, TF32><<<(unsigned)(2 * pairs), DT_THREADS, L::TOTAL, st>>>(tm_x, tm_w, p);
     WINO_CUDA_CHECK(cudaGetLastError());
     return WINO_OK;
 }
@@ -332,7 +367,8 @@ bool variant_override(int& bn, int& mt, int& resident) {
 
 bool direct_tc2_applies(const wino_conv_desc& d) {
     if (pair_mode() == 0) return false;
-    return d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC && d.dtype == WINO_BF16 && d.c % 64 == 0 && d.k % 16 == 0 && d.k >= 64;
+    if (!(d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC && d.k % 16 == 0 && d.k >= 64)) return false;
+    return d.dtype == WINO_BF16 ? d.c % 64 == 0 : d.dtype == WINO_TF32 ? d.c % 32 == 0 : false;
 }
 
 int launch_direct_tc2(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,
@@ -341,42 +377,46 @@ int launch_direct_tc2(const wino_conv_desc& d, const Geometry& g, const void* x,
     if (((uintptr_t)x | (uintptr_t)packed | (uintptr_t)y | (d.has_bias ? (uintptr_t)bias : 0)) & 15)
         return fail(WINO_E_BADARG, "direct conv: buffers (and the bias) must be 16-byte aligned");
     DtParams p;
-    p.bias = d.has_bias ? bias : nullptr; p.y = (__nv_bfloat16*)y;
+    p.bias = d.has_bias ? bias : nullptr; p.y = y;
     p.N = d.n; p.OH = g.oh; p.OW = g.ow; p.K = d.k; p.pad = d.pad; p.PH = g.ph; p.PW = g.pw;
     p.tiles_x = (g.ow + DT_TW - 1) / DT_TW; p.tiles_y = (g.oh + DT_TH - 1) / DT_TH;
-    p.cchunks = d.c / 64;
+    const bool tf32 = d.dtype == WINO_TF32;
+    const int es = tf32 ? 4 : 2;
+    p.cchunks = d.c / (128 / es);
     p.relu = d.relu; p.pool = d.pool2x2;
     int rc = status_word(&p.status);
     if (rc) return rc;
     int bn = d.k >= 256 ? 256 : d.k >= 128 ? 128 : 64, mt = 1, resident = 0;
     if (p.cchunks == 1 && bn <= 128) resident = 1;
-    else if (p.cchunks == 2 && bn == 128) resident = 1;
+    else if (p.cchunks == 2 && bn <= 128) resident = 1;
     if (bn == 128 && !resident) mt = 2;
     if (bn == 64) mt = 2;
     variant_override(bn, mt, resident);
     p.nblocks = (d.k + bn - 1) / bn;
-    p.idesc = make_idesc(OP_BF16, bn, 256);
+    p.idesc = make_idesc(tf32 ? OP_TF32 : OP_BF16, bn, 256);
     CUtensorMap tm_x, tm_w;
     {
         const unsigned long long dims[4] = {(unsigned long long)d.c, (unsigned long long)d.w, (unsigned long long)d.h, (unsigned long long)d.n};
-        const unsigned long long strides[3] = {d.c * 2ull, (unsigned long long)d.w * d.c * 2ull, (unsigned long long)d.h * d.w * d.c * 2ull};
-        const unsigned box[4] = {64u, (unsigned)DT_BOX_W, (unsigned)DT_BOX_H, 1u};
-        if ((rc = encode_tensor_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, x, dims, strides, box, true))) return rc;
+        const unsigned long long ues = (unsigned long long)es;
+        const unsigned long long strides[3] = {d.c * ues, (unsigned long long)d.w * d.c * ues, (unsigned long long)d.h * d.w * d.c * ues};
+        const unsigned box[4] = {(unsigned)(128 / es), (unsigned)DT_BOX_W, (unsigned)DT_BOX_H, 1u};
+        if ((rc = encode_tensor_map(&tm_x, tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, x, dims, strides, box, true))) return rc;
     }
     // each CTA of a pair loads half of the filter block's rows per tap
-    if ((rc = make_map_k128(&tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, packed, d.c, d.k, d.k, 9, bn / 2))) return rc;
+    if ((rc = make_map_k128(&tm_w, tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, es, packed, d.c, d.k, d.k, 9, bn / 2))) return rc;
     const int key = bn * 100 + mt * 10 + resident * (p.cchunks <= 2 ? p.cchunks : 9);
     switch (key) {
-        case 64 * 100 + 11:  return run2<64, 1, 6, 2, true, 1>(tm_x, tm_w, p, st);
-        case 64 * 100 + 21:  return run2<64, 2, 6, 2, true, 1>(tm_x, tm_w, p, st);
-        case 64 * 100 + 41:  return run2<64, 4, 8, 2, true, 1>(tm_x, tm_w, p, st);
-        case 128 * 100 + 11: return run2<128, 1, 6, 2, true, 1>(tm_x, tm_w, p, st);
-        case 128 * 100 + 21: return run2<128, 2, 6, 2, true, 1>(tm_x, tm_w, p, st);
-        case 128 * 100 + 12: return run2<128, 1, 3, 2, true, 2>(tm_x, tm_w, p, st);
-        case 64 * 100 + 20:  return run2<64, 2, 6, 9, false, 1>(tm_x, tm_w, p, st);
-        case 128 * 100 + 10: return run2<128, 1, 6, 6, false, 1>(tm_x, tm_w, p, st);
-        case 128 * 100 + 20: return run2<128, 2, 6, 6, false, 1>(tm_x, tm_w, p, st);
-        case 256 * 100 + 10: return run2<256, 1, 4, 6, false, 1>(tm_x, tm_w, p, st);
+        case 64 * 100 + 11:  return tf32 ? run2<64, 1, 6, 2, true, 1, true>(tm_x, tm_w, p, st) : run2<64, 1, 6, 2, true, 1, false>(tm_x, tm_w, p, st);
+        case 64 * 100 + 21:  return tf32 ? run2<64, 2, 6, 2, true, 1, true>(tm_x, tm_w, p, st) : run2<64, 2, 6, 2, true, 1, false>(tm_x, tm_w, p, st);
+        case 64 * 100 + 41:  return tf32 ? run2<64, 4, 8, 2, true, 1, true>(tm_x, tm_w, p, st) : run2<64, 4, 8, 2, true, 1, false>(tm_x, tm_w, p, st);
+        case 128 * 100 + 11: return tf32 ? run2<128, 1, 6, 2, true, 1, true>(tm_x, tm_w, p, st) : run2<128, 1, 6, 2, true, 1, false>(tm_x, tm_w, p, st);
+        case 128 * 100 + 21: return tf32 ? run2<128, 2, 6, 2, true, 1, true>(tm_x, tm_w, p, st) : run2<128, 2, 6, 2, true, 1, false>(tm_x, tm_w, p, st);
+        case 128 * 100 + 12: return tf32 ? run2<128, 1, 3, 2, true, 2, true>(tm_x, tm_w, p, st) : run2<128, 1, 3, 2, true, 2, false>(tm_x, tm_w, p, st);
+        case 64 * 100 + 22:  return tf32 ? run2<64, 2, 6, 2, true, 2, true>(tm_x, tm_w, p, st) : run2<64, 2, 6, 2, true, 2, false>(tm_x, tm_w, p, st);
+        case 64 * 100 + 20:  return tf32 ? run2<64, 2, 6, 9, false, 1, true>(tm_x, tm_w, p, st) : run2<64, 2, 6, 9, false, 1, false>(tm_x, tm_w, p, st);
+        case 128 * 100 + 10: return tf32 ? run2<128, 1, 6, 6, false, 1, true>(tm_x, tm_w, p, st) : run2<128, 1, 6, 6, false, 1, false>(tm_x, tm_w, p, st);
+        case 128 * 100 + 20: return tf32 ? run2<128, 2, 6, 6, false, 1, true>(tm_x, tm_w, p, st) : run2<128, 2, 6, 6, false, 1, false>(tm_x, tm_w, p, st);
+        case 256 * 100 + 10: return tf32 ? run2<256, 1, 4, 6, false, 1, true>(tm_x, tm_w, p, st) : run2<256, 1, 4, 6, false, 1, false>(tm_x, tm_w, p, st);
         default: return fail(WINO_E_UNSUPPORTED, "direct conv (CTA pairs): no kernel variant for this shape");
     }
 }

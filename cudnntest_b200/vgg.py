@@ -60,7 +60,9 @@ def kernel_model(batch, dtype="bf16", wino=4, layers=VGG16_CONV, layout="NHWC", 
             out["direct_thin_input"]["bytes"] += batch * (c * s * s + k * s * s) * s_io
             out["direct_thin_input"]["flops"] += batch * 2 * k * c * s * s * 9
             continue
-        if dtype == "bf16" and layout == "NHWC" and not forced_wino and c % 64 == 0 and (c <= 256 or s * s < 28 * 28) and k % 8 == 0:
+        direct = (dtype == "bf16" and c % 64 == 0 and (c <= 256 or s * s < 28 * 28) and k % 8 == 0) or \
+                 (dtype == "tf32" and c % 32 == 0 and c <= 256 and k % 16 == 0 and k >= 64)
+        if direct and not forced_wino:      # other layouts reach the same kernel through NHWC staging
             out["direct_tensor_core"]["bytes"] += batch * (c * s * s + k * o * o) * s_io
             out["direct_tensor_core"]["flops"] += batch * 2 * k * c * s * s * 9
             continue

@@ -164,6 +164,22 @@ def test_direct_tensor_core_path(cb, shape, pool):
     assert rel_l2(y0, oracle.conv_f64(x, wt, pad=0)) <= TOL_L2
 
 
+@pytest.mark.parametrize("shape,pool", [((2, 64, 32, 24, 64), True), ((1, 128, 20, 20, 128), False), ((3, 32, 17, 13, 80), True),
+                                        ((2, 256, 16, 24, 256), True), ((1, 96, 9, 9, 64), False), ((1, 64, 12, 12, 512), False)])
+@pytest.mark.parametrize("layout", ["NHWC", "NCHW", "CHWN"])
+def test_direct_tensor_core_path_tf32(cb, shape, pool, layout):
+    """Float storage with TF32 operands: C a multiple of 32 (up to 256) and K a multiple of 16 run the CTA-pair
+    implicit-GEMM kernel with kind::tf32 (NCHW / CHWN through NHWC staging): against the oracle and the Winograd path."""
+    n, c, h, w, k = shape
+    x, wt, b = make_inputs(n, c, h, w, k, seed=sum(shape) + 5)
+    ref = oracle.conv_f64(x, wt, bias=b, relu=True, pool=pool)
+    y = run_conv(x, wt, b, layout, dtype="tf32", relu=True, pool=pool)
+    assert y.shape == ref.shape
+    assert rel_l2(y, ref) <= TOL_L2
+    yw = run_conv(x, wt, b, layout, dtype="tf32", relu=True, pool=pool, wino=4)
+    assert rel_l2(yw, ref) <= TOL_L2
+
+
 def test_second_vgg_layer_full_size(cb):
     """64 -> 64 at 224 x 224 with the fused pool, BF16 NHWC, 2 images: against the oracle."""
     x, wt, b = make_inputs(2, 64, 224, 224, 64, seed=0xC0DE0042)
