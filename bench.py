@@ -162,7 +162,7 @@ def run_reference(args, rank):
     value = images * args.steps / total
     sample = "each step = %d image(s) through all 13 layers on the host cores (bounded sample of the %d-image batch)" % (
         images, args.batch)
-    print(json.dumps({
+    emit(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
@@ -374,13 +374,29 @@ def run_ours(args, rank, world, local_rank):
         import oracle
         oracle.build()
         out["cpu_baseline"] = cpu_baseline(args.layout, args.cpu_seconds)
-    print(json.dumps(out))
+    emit(json.dumps(out))
     if dist is not None:
         dist.destroy_process_group()
 
 
+_RESULT_FD = None
+
+
+def emit(line):
+    """Write the one result line to the process's real stdout."""
+    if _RESULT_FD is None:
+        print(line, flush=True)
+    else:
+        os.write(_RESULT_FD, (line + "\n").encode())
+
+
 def main():
+    global _RESULT_FD
     args = parse_args()
+    # stdout carries exactly one JSON line: anything a library prints there (NCCL's version banner, for one) goes to stderr
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
