@@ -6,7 +6,8 @@
 //   opt 0/1/2  this library, NCHW / NHWC / CHWN
 //   opt 3..6   cuDNN WINOGRAD_NONFUSED / WINOGRAD in NCHW, then in NHWC (FP32, FMA math), as in the reference
 //   opt 7/8    cuDNN's fastest forward algorithm in NCHW / NHWC for the chosen dtype ("cuDNN best")
-// Additions: dtype=fp32|tf32|bf16 (default fp32, the reference's arithmetic), wino=4|2, seed=, check=0|1,
+// Additions: dtype=fp32|tf32|bf16 (default fp32, the reference's arithmetic), wino=4|2|0 (0 = the engine's choice of
+// kernel per layer, the default for tf32 / bf16; 4 = F(4x4,3x3) Winograd, the default for fp32), seed=, check=0|1,
 // iters=.  With dtype=fp32 and opt 0..2 the timed call is layoutManager() through include/wino_compat.cuh, i.e.
 // the reference's own call with its semantics (filter transform inside, synchronous); a second figure times
 // the asynchronous surface (wino_conv_forward with pre-transformed filters), which is what tf32 / bf16 use.
@@ -27,7 +28,8 @@ int main(int argc, char** argv) {
     const int opt = (int)arg_int(argc, argv, "opt", 1);
     const int layer = (int)arg_int(argc, argv, "layer", 6);
     const int iters = (int)arg_int(argc, argv, "iters", 20);
-    const int wino = (int)arg_int(argc, argv, "wino", 4);
+    const std::string dts0 = arg_str(argc, argv, "dtype", "fp32");
+    const int wino = (int)arg_int(argc, argv, "wino", dts0 == "fp32" ? 4 : 0);
     const int check = (int)arg_int(argc, argv, "check", 1);
     const uint64_t seed = (uint64_t)arg_int(argc, argv, "seed", 0xC0DE);
     const std::string dts = arg_str(argc, argv, "dtype", "fp32");

@@ -1,4 +1,4 @@
-"""The C++ harness executables (layoutCompare, layoutTest, netTest) run, keep the reference's output format
+"""The C++ harness executables (layoutCompare, layoutTest, netTest, stageBench) run, keep the reference's output format
 ("time:<ms> ms" lines that comparison/test.sh greps for) and pass their own host-side checks."""
 import json
 import os
@@ -59,3 +59,14 @@ def test_net_test(mode):
     if s.get("unsupported"):
         return
     assert len(re.findall(r"time:[0-9.]+ ms", out)) == 3 and s["images_per_s"] > 0
+
+
+@pytest.mark.parametrize("dtype,layout,wino", [("bf16", "nhwc", 4), ("fp32", "nchw", 4), ("tf32", "chwn", 2)])
+def test_stage_bench(dtype, layout, wino):
+    """Per-stage micro-benchmark on the nine VGG-16 shapes: every staged pipeline passes its host-side check and the
+    weighted sums (the reference's weightedSum line and the JSON summary) are printed."""
+    out = run("stageBench", "batch=1", "dtype=" + dtype, "layout=" + layout, "wino=%d" % wino, "iters=2")
+    assert len(re.findall(r"^case \d: .* valid=yes", out, flags=re.M)) == 9
+    assert re.search(r"totalTime:[0-9.]+", out)
+    s = summary(out)
+    assert s["valid"] is True and s["weighted_us_vgg16"] > 0 and s["engine_weighted_us_vgg16"] > 0
