@@ -8,9 +8,14 @@
 //                (layoutManager + addBias + relu (+ pool), Network.h:456-519, :603-669)
 //   mode 3/4     cuDNN in NCHW / NHWC: fastest forward algorithm per layer + cudnnAddTensor +
 //                cudnnActivationForward (+ cudnnPoolingForward), i.e. Network.h:171-312, :314-444
-// plus dtype=fp32|tf32|bf16 (default bf16), rounds= (default 10).  The fully connected tail, softmax and the
-// accuracy count need the pretrained weights and ImageNet batches the reference does not ship; weights here are
-// seeded He-normal, the input uniform[-1,1].  Prints "time:<ms> ms" per round and a JSON summary.
+// plus dtype=fp32|tf32|bf16 (default bf16), rounds= (default 10), tail=0|1.  With tail=1 the classifier tail of the
+// reference (fc14 + ReLU, fc15 + ReLU, fc16, softmax, arg-max: Network.h:668-704) runs after the last round on the
+// output of conv13 (classifier_tail.h: cuBLAS GEMMs + small kernels), is checked against a host restatement for two
+// images and reports the top-1 classes.  The pretrained weights (./vggData/*.bin) and ImageNet batches the reference
+// reads are not shipped; they are used if present, otherwise weights are seeded He-normal and the input
+// uniform[-1,1] (so the classes mean nothing, the arithmetic is what is checked).  Prints "time:<ms> ms" per round
+// and a JSON summary.
+#include "classifier_tail.h"
 #include "cudnn_compare.h"
 #include "harness_common.h"
 
@@ -26,6 +31,7 @@ int main(int argc, char** argv) {
     const int n = (int)arg_int(argc, argv, "batch", 32);
     const int mode = (int)arg_int(argc, argv, "mode", 1);
     const int rounds = (int)arg_int(argc, argv, "rounds", 10);
+    const int tail = (int)arg_int(argc, argv, "tail", 0);
     const std::string dts = arg_str(argc, argv, "dtype", "bf16");
     const int dtype = dts == "bf16" ? WINO_BF16 : dts == "tf32" ? WINO_TF32 : WINO_FP32;
     HCHECK_CUDA(cudaSetDevice((int)arg_int(argc, argv, "device", 0)));
@@ -74,6 +80,7 @@ int main(int argc, char** argv) {
     HCHECK_CUDA(cudaEventCreate(&e1));
     std::vector<float> times;
     std::string what;
+    const void* final_out = nullptr;      // pooled output of conv13: (n, 512, 7, 7) in `layout`
 
     if (mode <= 2) {
         std::vector<wino_conv_desc> desc(13);
@@ -108,6 +115,7 @@ int main(int argc, char** argv) {
             if (r >= 2) times.push_back(ms);
         }
         HCHECK_WINO(wino_device_status());
+        final_out = act[12 & 1];
         what = "libwino: one fused conv+bias+ReLU(+pool) call per layer";
     } else {
         cudnnHandle_t handle;
@@ -186,6 +194,7 @@ int main(int argc, char** argv) {
             float ms;
             HCHECK_CUDA(cudaEventElapsedTime(&ms, e0, e1));
             if (r >= 2) times.push_back(ms);
+            final_out = cur;
         }
         what = "cuDNN: fastest forward algorithm per layer + AddTensor + ActivationForward (+ PoolingForward)";
         cudnnDestroy(handle);
@@ -200,8 +209,30 @@ int main(int argc, char** argv) {
     const double avg = sum / times.size();
     double flops = 0;
     for (const Layer& L : kVgg) flops += 2.0 * L.k * L.c * (double)L.s * L.s * 9;
+    std::string tail_json;
+    if (tail && final_out) {
+        ClassifierTail ct;
+        ct.init(n);
+        ct.forward(final_out, layout, dtype);          // warm-up (cuBLAS set-up)
+        HCHECK_CUDA(cudaDeviceSynchronize());
+        HCHECK_CUDA(cudaEventRecord(e0));
+        ct.forward(final_out, layout, dtype);
+        HCHECK_CUDA(cudaEventRecord(e1));
+        HCHECK_CUDA(cudaEventSynchronize(e1));
+        float tail_ms;
+        HCHECK_CUDA(cudaEventElapsedTime(&tail_ms, e0, e1));
+        bool ok0 = false, ok1 = false;
+        const double err0 = ct.check_image(0, &ok0), err1 = ct.check_image(n - 1, &ok1);
+        const std::vector<int> top1 = ct.top1();
+        for (int i = 0; i < n && i < 8; ++i) printf("Batch %d Resulting weights from Softmax:%d\n", i, top1[i]);
+        char buf[512];
+        snprintf(buf, sizeof(buf), ", \"tail_ms\": %.4f, \"tail_weights\": \"%s\", \"tail_max_abs_err\": %.3e, \"tail_top1_agree\": %s, \"top1_first\": %d",
+                 tail_ms, ct.from_files ? "vggData/*.bin" : "seeded", err0 > err1 ? err0 : err1, (ok0 && ok1) ? "true" : "false", top1[0]);
+        tail_json = buf;
+        if (!(err0 <= 1e-4 && err1 <= 1e-4)) printf("classifier tail error\n");
+    }
     printf("{\"harness\": \"netTest\", \"mode\": %d, \"batch\": %d, \"layout\": \"%s\", \"dtype\": \"%s\", \"ms_avg\": %.4f, \"ms_min\": %.4f, "
-           "\"images_per_s\": %.1f, \"tflops_direct_equiv\": %.2f, \"what\": \"%s\"}\n",
-           mode, n, layout_name(layout), dts.c_str(), avg, best, n / (avg * 1e-3), flops * n / avg / 1e9, what.c_str());
+           "\"images_per_s\": %.1f, \"tflops_direct_equiv\": %.2f, \"what\": \"%s\"%s}\n",
+           mode, n, layout_name(layout), dts.c_str(), avg, best, n / (avg * 1e-3), flops * n / avg / 1e9, what.c_str(), tail_json.c_str());
     return 0;
 }

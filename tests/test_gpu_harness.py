@@ -70,3 +70,14 @@ def test_stage_bench(dtype, layout, wino):
     assert re.search(r"totalTime:[0-9.]+", out)
     s = summary(out)
     assert s["valid"] is True and s["weighted_us_vgg16"] > 0 and s["engine_weighted_us_vgg16"] > 0
+
+
+@pytest.mark.parametrize("mode,dtype", [(1, "bf16"), (0, "fp32"), (2, "bf16")])
+def test_net_test_classifier_tail(mode, dtype):
+    """netTest tail=1: fc14/fc15/fc16 + softmax + arg-max on the conv stack's output, checked by the harness against
+    its host restatement (probabilities to 1e-4, same arg-max) for the first and the last image."""
+    out = run("netTest", "set", "batch=3", "mode=%d" % mode, "dtype=" + dtype, "rounds=1", "tail=1")
+    assert "classifier tail error" not in out
+    assert len(re.findall(r"Batch \d+ Resulting weights from Softmax:\d+", out)) == 3
+    s = summary(out)
+    assert s["tail_max_abs_err"] <= 1e-4 and s["tail_top1_agree"] is True and s["tail_ms"] > 0
