@@ -9,6 +9,8 @@
 // Rows beyond the tile count / filter count are predicated (zero loads, skipped stores); the reference
 // kernel has no bounds checks and needs M, N multiples of 128.
 // Bound: FP32 FFMA issue rate (2 * a*a * T * C * K flops), not memory.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace wino {
@@ -118,7 +120,8 @@ int launch_gemm_ffma(const float* v, const float* u, float* m, int batches, long
     const unsigned mb = (unsigned)((t_rows + GF_BM - 1) / GF_BM);
     ProfScope prof(STAGE_GEMM, st);
     count_launch();
-    if (k <= 64) {
+    static const int force_bn = [] { const char* e = getenv("WINO_FFMA_BN"); return e ? atoi(e) : 0; }();
+    if (force_bn ? force_bn == 64 : k <= 64) {
         dim3 grid(mb, (unsigned)((k + 63) / 64), (unsigned)batches);
         gemm_ffma_kernel<64><<<grid, 256, 0, st>>>(v, u, m, t_rows, tp, k, cp, kq);
     } else {

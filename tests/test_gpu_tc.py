@@ -229,3 +229,36 @@ def test_full_size_config3_bf16_nchw(cb):
     y = run_conv(x, wt, b, "NCHW", dtype="bf16", relu=True)
     ref = oracle.conv_f64(x[:4], wt, bias=b, relu=True)
     assert rel_l2(y[:4], ref) <= TOL_L2
+
+
+def test_vgg16_stack_layer_by_layer_and_graph(cb):
+    """The 13-layer stack (BF16 NHWC, one image): every layer's output against the oracle applied to the very
+    input that layer saw on the device (so the 5e-3 bar holds per layer, with the fused pool and the activation
+    ping-pong in the loop), then the same forward pass replayed from a CUDA graph gives the identical bits."""
+    import torch
+    from cudnntest_b200.vgg import VGG16ConvStack
+    stack = VGG16ConvStack(1, layout="NHWC", dtype="bf16", seed=0xC0DE0040)
+    gen = torch.Generator(device="cpu").manual_seed(7)
+    x = (torch.rand(stack.in_shape, generator=gen) * 2 - 1).to(torch.bfloat16).cuda()
+    cur = x
+    for i, conv in enumerate(stack.convs):
+        c, k, s, pool = stack.layers[i]
+        out = torch.empty(conv.out_shape, dtype=torch.bfloat16, device="cuda")
+        conv(cur, out=out)
+        x_np = oracle.from_layout(cur.float().cpu().numpy(), "NHWC")
+        w_np = stack.weights[i].to(torch.bfloat16).float().numpy()       # the filters as the device holds them
+        ref = oracle.conv_f64(x_np, w_np, bias=stack.biases[i].cpu().numpy(), relu=True, pool=bool(pool))
+        got = oracle.from_layout(out.float().cpu().numpy(), "NHWC")
+        assert got.shape == ref.shape
+        assert rel_l2(got, ref) <= TOL_L2, "layer %d (%d -> %d at %d)" % (i + 1, c, k, s)
+        cur = out
+    cb.device_status()
+    eager = stack(x).clone()
+    assert torch.equal(eager, cur)
+    graph, y = stack.capture(x)
+    y.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    cb.device_status()
+    assert torch.equal(y, eager)
+    assert stack.launches_per_forward >= 13
