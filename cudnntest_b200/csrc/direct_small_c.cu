@@ -161,10 +161,12 @@ __global__ void __launch_bounds__(128, 6) direct_small_c_kernel(const DCArgs a) 
         bool fast = false;
         if constexpr (sizeof(TIn) == 2 && CC == 3) {
             // Dense NHWC input with exactly three channels: the nine taps of a filter row are 18 contiguous bytes.
-            // Interior pixels fetch them as five aligned 32-bit words per row and shift them into place (the start
-            // is only 2-byte aligned); pixels on the left / right image border take the element-wise gather below.
-            // (the aligned words of a row may include the element after its ninth tap: not for the tensor's very last row)
-            fast = valid && nhwc3_in && ox >= a.pad && ox + 2 - a.pad < a.W &&
+            // A pixel fetches them as five aligned 32-bit words per row and shifts them into place (the start is only
+            // 2-byte aligned).  On the left / right image border the words still come from inside the tensor (the
+            // neighbouring row's end or start) and the taps that fall into the padding are masked to zero; only the
+            // pixels whose words would leave the tensor (its very first and last ones) take the element-wise gather.
+            const bool left_ok = ox - a.pad >= 0, right_ok = ox + 2 - a.pad < a.W;
+            fast = valid && nhwc3_in && !(n == 0 && oy - a.pad <= 0 && !left_ok) &&
                    !(n == a.N - 1 && oy + 2 - a.pad >= a.H - 1 && ox + 3 - a.pad >= a.W);
             if (fast) {
                 const long long m_pix = ((long long)n * a.H * a.W + (ox - a.pad)) * 3;       // element offset of tap (row 0 of the image, s = 0)
@@ -182,6 +184,8 @@ __global__ void __launch_bounds__(128, 6) direct_small_c_kernel(const DCArgs a) 
 #pragma unroll
                     for (int k = 0; k < 4; ++k) st[r][k] = __funnelshift_r(aw[k], aw[k + 1], sh);
                     st[r][4] = aw[4] >> sh;
+                    if (!left_ok) { st[r][0] = 0u; st[r][1] &= 0xFFFF0000u; }      // taps 0..2 (s = 0) are padding
+                    if (!right_ok) { st[r][3] = 0u; st[r][4] = 0u; }               // taps 6..8 (s = 2) are padding
                 }
                 // operand row: elements 0..8 = filter row 0, 9..17 = row 1, 18..26 = row 2, 27 = 1 (bias slot), 28..31 = 0
                 uint32_t w[16];
@@ -252,6 +256,8 @@ __global__ void __launch_bounds__(128, 6) direct_small_c_kernel(const DCArgs a) 
             uint8_t* wtile = a_tile + warp * 32 * 128;
             const int lane = tid & 31;
             const long long p0 = tile * 128 + warp * 32;
+            TOut* ybase = yout + p0 * a.K + k0;
+            const int rows_left = (int)(a.pixels - p0 < 32 ? a.pixels - p0 : 32);
 #pragma unroll
             for (int pass = 0; pass < PASSES; ++pass) {
 #pragma unroll
@@ -281,8 +287,8 @@ __global__ void __launch_bounds__(128, 6) direct_small_c_kernel(const DCArgs a) 
                 for (int i = 0; i < 8; ++i) {
                     const int j = i * 4 + (lane >> 3), cc = lane & 7;
                     const uint4 v4 = *reinterpret_cast<const uint4*>(wtile + j * 128 + ((cc ^ (j & 7)) << 4));
-                    if (p0 + j < a.pixels)
-                        *reinterpret_cast<uint4*>(yout + (p0 + j) * a.K + k0 + pass * 8 * PER + cc * PER) = v4;
+                    if (j < rows_left)
+                        *reinterpret_cast<uint4*>(ybase + j * a.K + pass * 8 * PER + cc * PER) = v4;
                 }
                 __syncwarp();
             }
