@@ -330,7 +330,7 @@ def run_ours(args, rank, world, local_rank):
     t_hbm, t_tc = byts / (peaks["hbm_gbs"] * 1e9), flops / (tpeak * 1e12)
     kernel_names = {"input_transform": "input_transform_nhwc_tma", "tile_gemm_plain": "gemm_tc_kernel" if args.dtype != "fp32" else "gemm_ffma_kernel",
                     "output_transform": "output_transform_direct", "tile_gemm_rowfused": "gemm_tc_z_kernel",
-                    "direct_thin_input": "direct_small_c_kernel", "direct_tensor_core": "direct_tc2_kernel"}
+                    "direct_thin_input": "direct_small_c_kernel", "direct_tensor_core": "direct_tc2t_kernel + direct_tc2_kernel"}
     if t_hbm >= t_tc or args.dtype == "fp32":
         achieved = byts / t_meas / 1e9
         roofline = {"kernel": kernel_names[dominant], "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",

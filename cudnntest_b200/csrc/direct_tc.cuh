@@ -31,4 +31,9 @@ bool direct_tc2_applies(const wino_conv_desc& d);
 int launch_direct_tc2(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,
                       cudaStream_t st);
 
+// CTA-pair kernel with the filters as the M operand, K >= 256 (direct_tc2t.cu)
+bool direct_tc2t_applies(const wino_conv_desc& d);
+int launch_direct_tc2t(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,
+                       cudaStream_t st);
+
 }  // namespace wino

@@ -374,6 +374,10 @@ bool direct_tc2_applies(const wino_conv_desc& d) {
 int launch_direct_tc2(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,
                       cudaStream_t st) {
     if (d.n == 0) return WINO_OK;
+    {
+        int obn, omt, ores;
+        if (direct_tc2t_applies(d) && !variant_override(obn, omt, ores)) return launch_direct_tc2t(d, g, x, packed, bias, y, st);
+    }
     if (((uintptr_t)x | (uintptr_t)packed | (uintptr_t)y | (d.has_bias ? (uintptr_t)bias : 0)) & 15)
         return fail(WINO_E_BADARG, "direct conv: buffers (and the bias) must be 16-byte aligned");
     DtParams p;
