@@ -67,10 +67,62 @@ __global__ void __launch_bounds__(256) transpose_batched_pairs_kernel(const uint
     }
 }
 
+// 2-byte elements with every extent, stride and pointer a multiple of 16 bytes: 64 x 64 element tiles moved as
+// 16-byte vectors on both sides.  The tile sits in shared memory as 64 rows of 32 words whose 16-byte chunks are XOR-ed
+// with (row / 8) % 8, which keeps both the row-wise 16-byte stores and the column-wise word reads conflict free;
+// a thread reads the word (two q values) of eight consecutive rows and re-pairs the halves into two 16-byte
+// vectors of eight r values each.
+__global__ void __launch_bounds__(256) transpose_batched_vec_kernel(const uint16_t* __restrict__ in, uint16_t* __restrict__ out, int R,
+                                                                    int Q, int qtiles, long long sb_in, long long sr_in,
+                                                                    long long sb_out, long long sq_out) {
+    __shared__ __align__(16) uint32_t tile[64][32];
+    const int qt = blockIdx.x % qtiles;
+    const long long b = blockIdx.x / qtiles;
+    const int q0 = qt * 64, r0 = blockIdx.y * 64;
+    const int t = threadIdx.x;
+    const uint16_t* src = in + b * sb_in;
+    uint16_t* dst = out + b * sb_out;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int row = t / 8 + 32 * u, chunk = t % 8;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r0 + row < R && q0 + 8 * chunk < Q) v = __ldg(reinterpret_cast<const uint4*>(src + (long long)(r0 + row) * sr_in + q0 + 8 * chunk));
+        *reinterpret_cast<uint4*>(&tile[row][(chunk ^ ((row >> 3) & 7)) * 4]) = v;
+    }
+    __syncthreads();
+    const int j = t % 8, qp = t / 8;              // r block of eight rows, pair of q values
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = tile[8 * j + i][qp ^ (j << 2)];
+    if (r0 + 8 * j < R) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int q = q0 + 2 * qp + e;
+            if (q < Q) {
+                const uint32_t sel = e ? 0x7632u : 0x5410u;     // high or low halves of a pair of words
+                const uint4 v = make_uint4(__byte_perm(w[0], w[1], sel), __byte_perm(w[2], w[3], sel), __byte_perm(w[4], w[5], sel),
+                                           __byte_perm(w[6], w[7], sel));
+                *reinterpret_cast<uint4*>(dst + (long long)q * sq_out + r0 + 8 * j) = v;
+            }
+        }
+    }
+}
+
 template <typename T>
 static int run_transpose(const void* in, void* out, long long B, long long R, long long Q, long long sb_in, long long sr_in,
                          long long sb_out, long long sq_out, cudaStream_t st) {
     if (B == 0 || R == 0 || Q == 0) return WINO_OK;
+    if (sizeof(T) == 2 && ((R | Q | sb_in | sr_in | sb_out | sq_out) & 7) == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+        const long long qt = (Q + 63) / 64, rt = (R + 63) / 64;
+        if (B * qt <= 0x7fffffffLL && rt <= 65535 && R <= 0x7fffffffLL && Q <= 0x7fffffffLL) {
+            dim3 grid((unsigned)(B * qt), (unsigned)rt);
+            count_launch();
+            transpose_batched_vec_kernel<<<grid, 256, 0, st>>>((const uint16_t*)in, (uint16_t*)out, (int)R, (int)Q, (int)qt, sb_in, sr_in,
+                                                                sb_out, sq_out);
+            WINO_CUDA_CHECK(cudaGetLastError());
+            return WINO_OK;
+        }
+    }
     if (sizeof(T) == 2 && ((R | Q | sb_in | sr_in | sb_out | sq_out) & 1) == 0 && (((uintptr_t)in | (uintptr_t)out) & 3) == 0) {
         const long long qt = (Q + 63) / 64, rt = (R + 63) / 64;
         if (B * qt <= 0x7fffffffLL && rt <= 65535 && R <= 0x7fffffffLL && Q <= 0x7fffffffLL) {

@@ -155,7 +155,8 @@ def test_padding_zero(cb):
 def test_relayout_bit_exact(cb, src, dst):
     import torch
     rng = np.random.default_rng(1)
-    for (n, c, h, w) in ((3, 37, 9, 13), (8, 72, 10, 14), (2, 130, 6, 66)):     # odd extents (scalar path) and even ones (paired path)
+    # odd extents (scalar path), even ones (paired path), multiples of 8 (16-byte vector path, ragged 64 x 64 tiles)
+    for (n, c, h, w) in ((3, 37, 9, 13), (8, 72, 10, 14), (2, 130, 6, 66), (8, 72, 8, 20), (16, 136, 12, 12)):
         x = rng.standard_normal((n, c, h, w)).astype(np.float32)
         for tdt in (torch.float32, torch.bfloat16):
             xs = to_dev(oracle.to_layout(x, src), tdt)
