@@ -11,6 +11,14 @@ pytestmark = pytest.mark.gpu
 BIN = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "cudnntest_b200", "harness", "bin")
 
 
+@pytest.fixture(scope="module", autouse=True)
+def harness_built():
+    """The executables are build products (git-ignored): compile them on the spot if this tree has none yet."""
+    if not all(os.path.exists(os.path.join(BIN, e)) for e in ("layoutCompare", "layoutTest", "netTest", "stageBench")):
+        import cudnntest_b200
+        cudnntest_b200.build()
+
+
 def run(exe, *args):
     p = subprocess.run([os.path.join(BIN, exe)] + list(args), capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
