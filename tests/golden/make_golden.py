@@ -37,7 +37,9 @@ def load(ref_root, layout):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <checkout of Elon-Wang/cudnnTest>")
+    ref_root = sys.argv[1]
     here = os.path.dirname(os.path.abspath(__file__))
     for li, layout in enumerate(("NCHW", "NHWC", "CHWN")):
         mod = load(ref_root, layout)
