@@ -28,13 +28,14 @@ namespace wino {
 
 namespace {
 
-template <int BN, int MT, int A_STAGES, int B_STAGES, bool B_RESIDENT, int RES_CHUNKS>
+template <int BN, int MT, int A_STAGES, int B_STAGES, bool B_RESIDENT, int RES_CHUNKS, bool STG = false>
 struct Dt2Smem {
     static constexpr int B_TILE = (BN / 2) * 128;          // this CTA's half of one tap of one 64-channel chunk
     static constexpr int A_OFF = 0;
     static constexpr int B_OFF = A_OFF + A_STAGES * DT_A_STRIDE;
     static constexpr int B_BYTES = (B_RESIDENT ? 9 * RES_CHUNKS : B_STAGES) * B_TILE;
-    static constexpr int BAR_OFF = B_OFF + B_BYTES;
+    static constexpr int STG_OFF = B_OFF + B_BYTES;        // optional store staging: 4 KiB per epilogue warp
+    static constexpr int BAR_OFF = STG_OFF + (STG ? DT_EPI_WARPS * 4096 : 0);
     static constexpr int TMEM_COLS = 512;                  // the whole tensor memory: one CTA per SM anyway
     static constexpr int ACC = TMEM_COLS / (MT * BN) < 4 ? TMEM_COLS / (MT * BN) : 4;   // accumulator stages
     static constexpr int NBARS = 2 * A_STAGES + 2 * B_STAGES + 2 * ACC + 1;
@@ -42,10 +43,12 @@ struct Dt2Smem {
     static constexpr int TOTAL = SLOT_OFF + 16 + 1024;
 };
 
-template <int BN, int MT, int A_STAGES, int B_STAGES, bool B_RESIDENT, int RES_CHUNKS, bool TF32>
+template <int BN, int MT, int A_STAGES, int B_STAGES, bool B_RESIDENT, int RES_CHUNKS, bool TF32, bool STG = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(DT_THREADS, 1)
-direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const DtParams p) {
-    using L = Dt2Smem<BN, MT, A_STAGES, B_STAGES, B_RESIDENT, RES_CHUNKS>;
+direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                  const __grid_constant__ CUtensorMap tm_y, const DtParams p) {
+    using L = Dt2Smem<BN, MT, A_STAGES, B_STAGES, B_RESIDENT, RES_CHUNKS, STG>;
+    static_assert(!STG || (BN == 128 && !TF32), "store staging exists for 128-filter blocks of bf16 outputs");
     static_assert(L::ACC >= 2, "accumulators are at least double-buffered");
     constexpr int ACC = L::ACC;
     constexpr int CPC = TF32 ? 32 : 64;      // channels per 128-byte chunk
@@ -210,6 +213,7 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         int as = 0;
         uint32_t aphase = 0;
         bool ok = true;
+        [[maybe_unused]] bool stg_pending = false;
         for (long long u = first; ok && u < total; u += step) {
             if (!mbar_wait_bounded(bar_tfull + 8 * as, aphase, abort_flag, p.status, DT_W_T_FULL)) ok = false;
             ok = __all_sync(0xffffffffu, ok);
@@ -298,7 +302,32 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                             w[e] = *reinterpret_cast<uint32_t*>(&m);
                         }
                     }
-                    if (writer) {
+                    if (STG && !p.pool) {
+                        // Unpooled outputs leave through the TMA unit: the warp lays its 32 pixels x 64 filters out as a
+                        // 128-byte-swizzled box (8 wide, 4 high) in its own staging tile and one lane stores it; the
+                        // box is clipped at the image and filter edges.  Stored from registers instead, every 16-byte
+                        // store instruction of a warp touches 32 different lines.
+                        uint8_t* stg = gen + L::STG_OFF + (warp - 2) * 4096;
+                        if (chunk == 0 && stg_pending) {       // the previous store must have read the tile
+                            if (lane == 0) tma_store_wait_read<0>();
+                            __syncwarp();
+                            stg_pending = false;
+                        }
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            *reinterpret_cast<uint4*>(stg + lane * 128 + (((chunk * 4 + c) ^ (lane & 7)) << 4)) =
+                                make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+                        if (chunk == CHUNKS - 1) {
+                            fence_async_shared();
+                            __syncwarp();
+                            if (lane == 0 && valid) {
+                                tma_store_4d(&tm_y, base + L::STG_OFF + (warp - 2) * 4096, nb * BN + half * (BN / 2), tx * DT_TW,
+                                             ty * DT_TH + 4 * quarter, n);
+                                tma_store_commit();
+                            }
+                            stg_pending = true;
+                        }
+                    } else if (writer) {
                         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.y) + pix * p.K + k0;
                         if (k0 + 32 <= p.K && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
@@ -314,6 +343,7 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             }
             if (++as == ACC) { as = 0; aphase ^= 1; }
         }
+        if (STG && lane == 0) tma_store_wait_all();      // staged outputs are on their way before the CTA leaves
     }
 
     // neither CTA may leave (or give back tensor memory) while its partner can still read its shared memory,
@@ -326,16 +356,16 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     }
 }
 
-template <int BN, int MT, int A_STAGES, int B_STAGES, bool B_RESIDENT, int RES_CHUNKS, bool TF32>
-int run2(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const DtParams& p, cudaStream_t st) {
-    using L = Dt2Smem<BN, MT, A_STAGES, B_STAGES, B_RESIDENT, RES_CHUNKS>;
+template <int BN, int MT, int A_STAGES, int B_STAGES, bool B_RESIDENT, int RES_CHUNKS, bool TF32, bool STG = false>
+int run2(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const DtParams& p, cudaStream_t st, const CUtensorMap* tm_y = nullptr) {
+    using L = Dt2Smem<BN, MT, A_STAGES, B_STAGES, B_RESIDENT, RES_CHUNKS, STG>;
     static_assert(L::TOTAL <= 232448, "shared memory budget of one CTA exceeded");
     static std::once_flag once[64];
     int dev = 0;
     WINO_CUDA_CHECK(cudaGetDevice(&dev));
     cudaError_t attr_err = cudaSuccess;
     std::call_once(once[dev & 63], [&] {
-        attr_err = cudaFuncSetAttribute(direct_tc2_kernel<BN, MT, A_STAGES, B_STAGES, B_RESIDENT, RES_CHUNKS, TF32>,
+        attr_err = cudaFuncSetAttribute(direct_tc2_kernel<BN, MT, A_STAGES, B_STAGES, B_RESIDENT, RES_CHUNKS, TF32, STG>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     });
     WINO_CUDA_CHECK(attr_err);
@@ -347,7 +377,8 @@ int run2(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const DtParams& p, cu
     if (pairs < 1) pairs = p.nblocks;
     ProfScope prof(STAGE_DIRECT_TC, st);
     count_launch();
-    direct_tc2_kernel<BN, MT, A_STAGES, B_STAGES, B_RESIDENT, RES_CHUNKS, TF32><<<(unsigned)(2 * pairs), DT_THREADS, L::TOTAL, st>>>(tm_x, tm_w, p);
+    direct_tc2_kernel<BN, MT, A_STAGES, B_STAGES, B_RESIDENT, RES_CHUNKS, TF32, STG><<<(unsigned)(2 * pairs), DT_THREADS, L::TOTAL, st>>>(
+        tm_x, tm_w, tm_y ? *tm_y : tm_x, p);
     WINO_CUDA_CHECK(cudaGetLastError());
     return WINO_OK;
 }
@@ -409,6 +440,16 @@ int launch_direct_tc2(const wino_conv_desc& d, const Geometry& g, const void* x,
     // each CTA of a pair loads half of the filter block's rows per tap
     if ((rc = make_map_k128(&tm_w, tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, es, packed, d.c, d.k, d.k, 9, bn / 2))) return rc;
     const int key = bn * 100 + mt * 10 + resident * (p.cchunks <= 2 ? p.cchunks : 9);
+    static const bool stage_off = [] { const char* e = getenv("WINO_DIRECT_TC_TMA_STORE"); return e && e[0] == '0'; }();
+    if (!stage_off && !tf32 && !d.pool2x2 && key == 128 * 100 + 11 && d.k % 8 == 0) {
+        // unpooled bf16 output of a resident 64-channel layer (64 -> 128 of VGG-16): stores staged through the TMA unit
+        CUtensorMap tm_y;
+        const unsigned long long dims[4] = {(unsigned long long)d.k, (unsigned long long)g.ow, (unsigned long long)g.oh, (unsigned long long)d.n};
+        const unsigned long long strides[3] = {d.k * 2ull, (unsigned long long)g.ow * d.k * 2ull, (unsigned long long)g.oh * g.ow * d.k * 2ull};
+        const unsigned box[4] = {64u, (unsigned)DT_TW, 4u, 1u};
+        if ((rc = encode_tensor_map(&tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, y, dims, strides, box, true))) return rc;
+        return run2<128, 1, 4, 2, true, 1, false, true>(tm_x, tm_w, p, st, &tm_y);
+    }
     switch (key) {
         case 64 * 100 + 11:  return tf32 ? run2<64, 1, 6, 2, true, 1, true>(tm_x, tm_w, p, st) : run2<64, 1, 6, 2, true, 1, false>(tm_x, tm_w, p, st);
         case 64 * 100 + 21:  return tf32 ? run2<64, 2, 6, 2, true, 1, true>(tm_x, tm_w, p, st) : run2<64, 2, 6, 2, true, 1, false>(tm_x, tm_w, p, st);

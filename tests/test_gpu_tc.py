@@ -146,13 +146,15 @@ def test_thin_input_direct_path(cb, dtype, layout, shape):
                                         ((2, 128, 40, 9, 200), True), ((1, 192, 9, 9, 64), False), ((2, 256, 16, 24, 256), False),
                                         ((1, 512, 14, 14, 512), True), ((3, 256, 12, 20, 144), True), ((1, 320, 6, 6, 96), False),
                                         ((5, 64, 40, 24, 128), True), ((1, 64, 8, 16, 64), False), ((3, 64, 30, 20, 384), True),
-                                        ((1, 128, 7, 9, 256), False), ((2, 64, 22, 16, 256), True), ((1, 64, 10, 8, 256), False)])
+                                        ((1, 128, 7, 9, 256), False), ((2, 64, 22, 16, 256), True), ((1, 64, 10, 8, 256), False),
+                                        ((2, 64, 19, 21, 128), False), ((1, 64, 13, 10, 144), False)])
 def test_direct_tensor_core_path(cb, shape, pool):
     """NHWC BF16 layers with C a multiple of 64 and no explicit tile size run the implicit-GEMM kernels (halo box +
     shifted descriptors; CTA pairs when K is a multiple of 16, the single-CTA kernel otherwise): against the oracle,
     against the Winograd path, with and without the fused pool, ragged edges, every filter-block width, resident and
     streamed filters, an odd number of tiles (a pair's spare tile is computed and dropped); K >= 256 takes the
-    filters-as-M kernel with every pixel tile height (8 ... 16) and a half-empty filter block (K = 384)."""
+    filters-as-M kernel with every pixel tile height (8 ... 16) and a half-empty filter block (K = 384); unpooled
+    64 -> 128 / 144 layers leave through staged TMA stores that are clipped at the image and filter edges."""
     n, c, h, w, k = shape
     x, wt, b = make_inputs(n, c, h, w, k, seed=sum(shape) + 3)
     ref = oracle.conv_f64(x, wt, bias=b, relu=True, pool=pool)
