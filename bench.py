@@ -340,6 +340,9 @@ def run_ours(args, rank, world, local_rank):
         roofline = {"kernel": kernel_names[dominant], "bound": "tensor", "achieved": achieved, "peak": tpeak, "unit": "TFLOP/s",
                     "frac": achieved / tpeak, "traffic": None,
                     "peak_source": peaks["source"] + " sustained bf16 cuBLAS" + (" halved for tf32" if args.dtype == "tf32" else "")}
+    if args.dtype == "fp32" and dominant == "tile_gemm_plain":
+        roofline["note"] = ("the exact-FP32 tile GEMM is bound by the FP32 FMA pipe, which this object's hbm|tensor vocabulary does not "
+                            "name: %.1f TFLOP/s of a nominal 74.4 (148 SMs x 128 lanes x 2 x 1.965 GHz)" % (flops / t_meas / 1e12))
     # DRAM traffic per launch: ncu's dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of this kernel
     # (profiles/ncu_<kernel>_vgg16_bf16_nhwc_batch32.md) divided by that launch's algorithmic bytes, applied to the
     # average algorithmic bytes per launch here.  Reads match the algorithmic bytes; output still dirty in the 126 MB L2
