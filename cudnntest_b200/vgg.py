@@ -56,7 +56,7 @@ def kernel_model(batch, dtype="bf16", wino=4, layers=VGG16_CONV, layout="NHWC", 
                                                  "output_transform", "direct_thin_input", "direct_tensor_core")}
     for (c, k, s, pool) in layers:
         o = s // 2 if pool else s
-        if c <= 3 and not pool and dtype != "fp32" and not forced_wino:
+        if c <= 3 and not pool and not forced_wino:
             out["direct_thin_input"]["bytes"] += batch * (c * s * s + k * s * s) * s_io
             out["direct_thin_input"]["flops"] += batch * 2 * k * c * s * s * 9
             continue
