@@ -49,12 +49,12 @@ def load_peaks():
         return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
-def engine_runs_winograd(dtype, layout, c, k, s, wino):
+def engine_runs_winograd(dtype, layout, n, c, k, s, wino):
     """Mirror of the library's per-layer choice for these shapes (C a multiple of 64, K a multiple of 16)."""
     if wino or dtype == "fp32":
         return True
     if dtype == "bf16":
-        return not (c <= 256 or s * s < 28 * 28)
+        return not (c <= 256 or s * s < 28 * 28 or n * s * s < 128 * 28 * 28)
     return c > 256      # tf32
 
 
@@ -87,7 +87,7 @@ def run_variant(cfg_id, cfg, dtype, layout, wino, iters, peaks, flush):
     ms = times[len(times) // 2]
     flops = 2.0 * n * k * c * s * s * 9
     byts = (n * c * s * s + 9 * k * c + n * k * s * s) * es + (4 * k if cfg["bias"] else 0)
-    winograd = engine_runs_winograd(dtype, layout, c, k, s, wino)
+    winograd = engine_runs_winograd(dtype, layout, n, c, k, s, wino)
     m = wino or 4
     arithmetic = 2.0 * (m + 2) ** 2 * n * math.ceil(s / m) ** 2 * c * k if winograd else flops
     peak = {"bf16": peaks["bf16_tflops"], "tf32": peaks["bf16_tflops"] / 2, "fp32": FFMA_TFLOPS_NOMINAL}[dtype]

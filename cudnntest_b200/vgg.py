@@ -47,8 +47,8 @@ def winograd_gemm_flops_per_image(wino=4, layers=VGG16_CONV):
 
 def kernel_model(batch, dtype="bf16", wino=4, layers=VGG16_CONV, layout="NHWC", forced_wino=False):
     """Algorithmic bytes and flops of one forward pass per kernel class, following the engine's per-layer choice
-    for NHWC: C <= 3 (no pool): thin-input direct kernel; BF16 with C a multiple of 64 and (C <= 256 or an image
-    smaller than 28 x 28): direct tensor-core kernel; other tensor-core layers with C <= 128: row-fused tile GEMM
+    for NHWC: C <= 3 (no pool): thin-input direct kernel; BF16 with C a multiple of 64 and (C <= 256, an image
+    smaller than 28 x 28 or fewer than 128 * 784 pixels in the batch): direct tensor-core kernel; other tensor-core layers with C <= 128: row-fused tile GEMM
     (products Z, a*m planes, half for bf16); otherwise the plain tile GEMM (products M, a*a float planes)."""
     a, m = wino + 2, wino
     s_io = 2 if dtype == "bf16" else 4
@@ -60,7 +60,8 @@ def kernel_model(batch, dtype="bf16", wino=4, layers=VGG16_CONV, layout="NHWC", 
             out["direct_thin_input"]["bytes"] += batch * (c * s * s + k * s * s) * s_io
             out["direct_thin_input"]["flops"] += batch * 2 * k * c * s * s * 9
             continue
-        direct = (dtype == "bf16" and c % 64 == 0 and (c <= 256 or s * s < 28 * 28) and k % 8 == 0) or \
+        direct = (dtype == "bf16" and c % 64 == 0 and k % 8 == 0 and
+                  (c <= 256 or s * s < 28 * 28 or batch * s * s < 128 * 28 * 28)) or \
                  (dtype == "tf32" and c % 32 == 0 and c <= 256 and k % 16 == 0 and k >= 64)
         if direct and not forced_wino:      # other layouts reach the same kernel through NHWC staging
             out["direct_tensor_core"]["bytes"] += batch * (c * s * s + k * o * o) * s_io
