@@ -150,6 +150,7 @@ def run_reference(args, rank):
         return
     import oracle
     oracle.build()
+    oracle.set_num_threads(len(os.sched_getaffinity(0)))    # all host cores, whatever the launcher put in OMP_NUM_THREADS
     config = workload_config(args)
     rate, dt = cpu_stack_images_per_s(args.layout, 1)       # sizing probe
     images = int(max(1, min(16, 20.0 / max(dt, 1e-3) / max(args.steps + args.warmup, 1))))
@@ -376,6 +377,7 @@ def run_ours(args, rank, world, local_rank):
     if world == 1 and not args.no_cpu_baseline:
         import oracle
         oracle.build()
+        oracle.set_num_threads(len(os.sched_getaffinity(0)))
         out["cpu_baseline"] = cpu_baseline(args.layout, args.cpu_seconds)
     emit(json.dumps(out))
     if dist is not None:

@@ -126,3 +126,8 @@ def maxpool2x2(x, layout="NCHW"):
 
 def num_threads():
     return int(_load().ref_num_threads())
+
+
+def set_num_threads(n):
+    """Threads of the float32 baseline (conv_f32); the environment's OMP_NUM_THREADS is only the default."""
+    _load().ref_set_num_threads(int(n))
