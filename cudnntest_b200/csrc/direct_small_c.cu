@@ -19,6 +19,7 @@
 // Several CTAs share an SM so one CTA's gather overlaps another's MMA and stores.  Bound: HBM, by the output
 // write (N*K*OH*OW elements); the input is read once from HBM and nine times from L1/L2.
 #include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -40,6 +41,7 @@ struct DCArgs {
     long long pixels;      // N * oh * ow
     int relu;
     int n_fastest;         // pixel order of a tile: images fastest (CHWN) or columns fastest
+    int tma_store;         // dense NHWC 2-byte output: tiles leave through TMA stores of the staging rows
     uint32_t idesc;
     Strides sx, sw, sy;
     int* status;
@@ -85,12 +87,14 @@ struct OperandRow<float> {
 };
 
 template <typename TIn, typename TOut, int CC>
-__global__ void __launch_bounds__(128, 6) direct_small_c_kernel(const DCArgs a) {
+__global__ void __launch_bounds__(128, 5) direct_small_c_kernel(const __grid_constant__ CUtensorMap tm_y, const DCArgs a) {
     using Row = OperandRow<TIn>;
     using raw_t = typename Row::raw_t;
     constexpr int BIAS_COL = 9 * CC;        // first unused contraction slot: pixel rows hold 1 there, filter rows the bias
     static_assert(BIAS_COL < 32, "the contraction is padded to 32 and one spare slot carries the bias");
-    __shared__ __align__(1024) uint8_t a_tile[128 * 128];
+    // two operand tiles used alternately: while the MMA / the output store of one tile still reads its buffer, the
+    // next tile is gathered into the other
+    __shared__ __align__(1024) uint8_t a_tiles[2][128 * 128];
     __shared__ __align__(1024) uint8_t b_tile[64 * 128];
     __shared__ __align__(8) unsigned long long bar_storage;
     __shared__ uint32_t tmem_slot;
@@ -126,7 +130,7 @@ __global__ void __launch_bounds__(128, 6) direct_small_c_kernel(const DCArgs a) 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
-    const uint32_t a_s = smem_u32(a_tile), b_s = smem_u32(b_tile);
+    const uint32_t a_s0 = smem_u32(a_tiles[0]), b_s = smem_u32(b_tile);
     const TIn* __restrict__ xin = reinterpret_cast<const TIn*>(a.x);
     TOut* __restrict__ yout = reinterpret_cast<TOut*>(a.y);
 
@@ -136,7 +140,15 @@ __global__ void __launch_bounds__(128, 6) direct_small_c_kernel(const DCArgs a) 
     // dense NHWC input with exactly three channels, 4-byte aligned
     const bool nhwc3_in = !a.n_fastest && a.C == 3 && a.sx.c == 1 && a.sx.w == 3 && a.sx.h == 3LL * a.W && a.sx.n == 3LL * a.W * a.H &&
                           (reinterpret_cast<uintptr_t>(a.x) & 3) == 0 && a.W >= 4 && a.pad <= 1;
-    for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const bool use_tma = sizeof(TOut) == 2 && a.tma_store && dense_nhwc;
+    int buf = 0;
+    for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x, buf ^= 1) {
+        uint8_t* a_tile = a_tiles[buf];
+        const uint32_t a_s = a_s0 + (uint32_t)buf * (128 * 128);
+        if (use_tma) {          // the store that last read this buffer (two tiles ago) must be done with it
+            if ((tid & 31) == 0) tma_store_wait_read<1>();
+            __syncwarp();
+        }
         const long long p = tile * 128 + tid;
         const bool valid = p < a.pixels;
         int n = 0, oy = 0, ox = 0;
@@ -282,6 +294,15 @@ __global__ void __launch_bounds__(128, 6) direct_small_c_kernel(const DCArgs a) 
                     }
                     *reinterpret_cast<uint4*>(wtile + lane * 128 + ((c ^ (lane & 7)) << 4)) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
                 }
+                if (use_tma) {      // the staging rows are already a 128-byte-swizzled box: one lane hands them to the TMA unit
+                    fence_async_shared();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tm_y, smem_u32(wtile), k0, (int)p0);
+                        tma_store_commit();
+                    }
+                    continue;
+                }
                 __syncwarp();
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -413,13 +434,25 @@ __global__ void __launch_bounds__(128) direct_small_c_fp32_kernel(const DCArgs a
 }
 
 template <typename TIn, typename TOut>
-int run(const DCArgs& a, cudaStream_t st) {
+int run(DCArgs a, cudaStream_t st) {
     const long long tiles = (a.pixels + 127) / 128;
-    const long long max_ctas = 6LL * sm_count();
+    const long long max_ctas = 5LL * sm_count();
     dim3 grid((unsigned)(tiles < max_ctas ? tiles : max_ctas), (unsigned)((a.K + 63) / 64));
+    // dense NHWC 2-byte output seen as a [pixels][K] matrix: 32-pixel x 64-filter boxes, 128-byte swizzle
+    CUtensorMap tm_y;
+    memset(&tm_y, 0, sizeof(tm_y));
+    a.tma_store = 0;
+    static const bool tma_off = [] { const char* e = getenv("WINO_THIN_TMA_STORE"); return e && e[0] == '0'; }();
+    if (!tma_off && sizeof(TOut) == 2 && !a.n_fastest && a.sy.c == 1 && a.sy.w == a.K && a.sy.h == (long long)a.ow * a.K &&
+        a.sy.n == (long long)a.oh * a.ow * a.K && a.K % 8 == 0 && a.pixels < (1LL << 31) && ((uintptr_t)a.y & 15) == 0) {
+        const unsigned long long dims[2] = {(unsigned long long)a.K, (unsigned long long)a.pixels};
+        const unsigned long long strides[1] = {(unsigned long long)a.K * 2ull};
+        const unsigned box[2] = {64u, 32u};
+        if (encode_tensor_map(&tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y, dims, strides, box, true) == WINO_OK) a.tma_store = 1;
+    }
     ProfScope prof(STAGE_DIRECT, st);
     count_launch();
-    direct_small_c_kernel<TIn, TOut, 3><<<grid, 128, 0, st>>>(a);
+    direct_small_c_kernel<TIn, TOut, 3><<<grid, 128, 0, st>>>(tm_y, a);
     WINO_CUDA_CHECK(cudaGetLastError());
     return WINO_OK;
 }
