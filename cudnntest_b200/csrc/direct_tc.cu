@@ -302,7 +302,7 @@ bool direct_tc_applies(const wino_conv_desc& d) {
     // buffers are HBM-bound); at 512 channels Winograd's 4x fewer multiplies win, except on small images
     // (14 x 14) and small batches (fewer than 128 images of 28 x 28) where its tile GEMMs are too small to fill the
     // machine (512 -> 512 at 28 x 28, direct / Winograd: batch 64 0.162 / 0.179 ms, 128 0.319 / 0.317, 256 0.636 / 0.61).
-    static const int max_c = [] { const char* e = getenv("WINO_DIRECT_TC_MAXC"); return e ? atoi(e) : -1; }();
+    static const int max_c = [] { const char* e = getenv("WINO_DIRECT_TC_MAXC"); return (e && *e) ? atoi(e) : -1; }();
     if (!(d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC && d.wino == 0)) return false;
     if (d.dtype == WINO_TF32) {
         // float storage, TF32 operands: CTA-pair kernel only (32 channels per 128-byte chunk).  At half the tensor rate
