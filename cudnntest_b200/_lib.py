@@ -14,11 +14,11 @@ _SO = os.path.join(_HERE, "libwino.so")
 _HEADER = os.path.join(os.path.dirname(_HERE), "include", "wino.h")
 
 NCHW, NHWC, CHWN = 0, 1, 2
-FP32, TF32, BF16 = 0, 1, 2
+FP32, TF32, BF16, FP32X3 = 0, 1, 2, 3
 OPERAND_AUTO, OPERAND_BF16, OPERAND_F16 = 0, 1, 2
 OK, E_BADARG, E_UNSUPPORTED, E_WORKSPACE, E_CUDA, E_TIMEOUT = 0, -1, -2, -3, -4, -5
 LAYOUT_CODES = {"NCHW": NCHW, "NHWC": NHWC, "CHWN": CHWN}
-DTYPE_CODES = {"fp32": FP32, "tf32": TF32, "bf16": BF16}
+DTYPE_CODES = {"fp32": FP32, "tf32": TF32, "bf16": BF16, "fp32x3": FP32X3}
 
 
 class WinoError(RuntimeError):

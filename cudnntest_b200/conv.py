@@ -9,7 +9,7 @@ import torch
 from . import _lib
 from ._lib import ConvDesc, LAYOUT_CODES, DTYPE_CODES, check, lib
 
-_TORCH_DTYPE = {_lib.FP32: torch.float32, _lib.TF32: torch.float32, _lib.BF16: torch.bfloat16}
+_TORCH_DTYPE = {_lib.FP32: torch.float32, _lib.TF32: torch.float32, _lib.BF16: torch.bfloat16, _lib.FP32X3: torch.float32}
 
 
 def _code(table, v):

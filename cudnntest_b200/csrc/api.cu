@@ -90,6 +90,7 @@ int make_geometry(const wino_conv_desc* d, Geometry* g) {
     switch (d->dtype) {
         case WINO_FP32: g->operand = OP_F32; g->esize_io = 4; g->esize_op = 4; break;
         case WINO_TF32: g->operand = OP_TF32; g->esize_io = 4; g->esize_op = 4; break;
+        case WINO_FP32X3: g->operand = OP_TF32X3; g->esize_io = 4; g->esize_op = 4; break;
         case WINO_BF16:
             g->esize_io = 2; g->esize_op = 2;
             if (d->operand == WINO_OPERAND_AUTO) g->operand = OP_F16;
@@ -108,6 +109,7 @@ int make_geometry(const wino_conv_desc* d, Geometry* g) {
     g->bnx = (g->ow + g->m - 1) / g->m;
     g->tiles_img = g->bny * g->bnx;
     g->cp = round_up(d->c, 8);
+    g->crow = g->operand == OP_TF32X3 ? 2 * g->cp : g->cp;
     g->kq = round_up(d->k, 8);
     // What wino_conv_forward's tile GEMM writes.  The exact-FP32 path keeps the raw products M.  The tensor-core
     // paths write the row-transformed products Z (float for TF32, half for BF16 storage) when the layer is bound
@@ -115,7 +117,7 @@ int make_geometry(const wino_conv_desc* d, Geometry* g) {
     // operands and the 128-filter tiles of the plain kernel win.  WINO_ROWFUSE=0/1 forces either choice.
     {
         static const int force = [] { const char* e = getenv("WINO_ROWFUSE"); return e ? atoi(e) : -1; }();
-        const bool fuse = g->operand != OP_F32 && (force >= 0 ? force != 0 : d->c <= 128);
+        const bool fuse = g->operand != OP_F32 && g->operand != OP_TF32X3 && (force >= 0 ? force != 0 : d->c <= 128);
         g->prod_kind = !fuse ? 0 : g->operand == OP_TF32 ? 1 : 2;
     }
     g->prod_planes = g->prod_kind == 0 ? g->a * g->a : g->a * g->m;
@@ -133,7 +135,7 @@ static long long slab_budget_bytes() {
 }
 
 long long per_image_bytes(const Geometry& g) {
-    return (long long)g.tiles_img * ((long long)g.a * g.a * g.cp * g.esize_op + (long long)g.prod_planes * g.kq * g.esize_prod);
+    return (long long)g.tiles_img * ((long long)g.a * g.a * g.crow * g.esize_op + (long long)g.prod_planes * g.kq * g.esize_prod);
 }
 
 // images per slab
@@ -149,7 +151,7 @@ static int slab_images(const wino_conv_desc& d, const Geometry& g) {
 long long tile_rows(const Geometry& g, int ns) { return round_up_ll((long long)ns * g.tiles_img, 128); }
 
 size_t v_bytes(const Geometry& g, long long tp) {
-    return (size_t)round_up_ll((long long)g.a * g.a * tp * g.cp * g.esize_op, 1024);
+    return (size_t)round_up_ll((long long)g.a * g.a * tp * g.crow * g.esize_op, 1024);
 }
 size_t m_bytes(const Geometry& g, long long tp) {
     return (size_t)round_up_ll((long long)g.a * g.a * tp * g.kq * 4, 1024);
@@ -174,7 +176,7 @@ int run_conv_gemm(const Geometry& g, const void* v, const void* u, void* prod, i
 
 // stage-level entry points of the row-fused pair use Z whatever the layer width
 static bool force_rowfused(Geometry* g) {
-    if (g->operand == OP_F32) return false;
+    if (g->operand == OP_F32 || g->operand == OP_TF32X3) return false;
     g->prod_kind = g->operand == OP_TF32 ? 1 : 2;
     g->prod_planes = g->a * g->m;
     g->esize_prod = g->prod_kind == 2 ? 2 : 4;
@@ -241,7 +243,7 @@ int wino_device_status(void) {
 size_t wino_filter_bytes(const wino_conv_desc* d) {
     Geometry g;
     if (make_geometry(d, &g) != WINO_OK) return 0;
-    const size_t wino = (size_t)g.a * g.a * d->k * g.cp * g.esize_op;
+    const size_t wino = (size_t)g.a * g.a * d->k * g.crow * g.esize_op;
     // thin-input layers keep packed raw filters instead (always smaller); report the larger so either path fits
     size_t need = wino;
     if (direct_small_c_applies(*d) && direct_small_c_filter_bytes(*d) > need) need = direct_small_c_filter_bytes(*d);
@@ -266,7 +268,7 @@ long long wino_stage_tile_rows(const wino_conv_desc* d, int ns) {
 int wino_stage_cp(const wino_conv_desc* d) {
     Geometry g;
     if (make_geometry(d, &g) != WINO_OK) return -1;
-    return g.cp;
+    return g.crow;
 }
 
 int wino_stage_kq(const wino_conv_desc* d) {
@@ -411,7 +413,7 @@ int wino_layout_convert(int layout_src, int layout_dst, int n, int c, int h, int
                         wino_stream_t stream) {
     if (!layout_ok(layout_src) || !layout_ok(layout_dst)) return fail(WINO_E_BADARG, "layout convert: bad layout code");
     if (n < 0 || c < 0 || h < 0 || w < 0) return fail(WINO_E_BADARG, "layout convert: negative extent");
-    if (dtype != WINO_FP32 && dtype != WINO_TF32 && dtype != WINO_BF16) return fail(WINO_E_BADARG, "layout convert: bad dtype %d", dtype);
+    if (dtype != WINO_FP32 && dtype != WINO_TF32 && dtype != WINO_BF16 && dtype != WINO_FP32X3) return fail(WINO_E_BADARG, "layout convert: bad dtype %d", dtype);
     if ((long long)n * c * h * w == 0) return WINO_OK;
     if (!in || !out) return fail(WINO_E_BADARG, "layout convert: NULL pointer");
     int rc = check_device();
@@ -422,7 +424,7 @@ int wino_layout_convert(int layout_src, int layout_dst, int n, int c, int h, int
 int wino_maxpool2x2(int layout, int n, int c, int h, int w, int dtype, const void* in, void* out, wino_stream_t stream) {
     if (!layout_ok(layout)) return fail(WINO_E_BADARG, "maxpool: bad layout code");
     if (n < 0 || c < 0 || h < 0 || w < 0) return fail(WINO_E_BADARG, "maxpool: negative extent");
-    if (dtype != WINO_FP32 && dtype != WINO_TF32 && dtype != WINO_BF16) return fail(WINO_E_BADARG, "maxpool: bad dtype %d", dtype);
+    if (dtype != WINO_FP32 && dtype != WINO_TF32 && dtype != WINO_BF16 && dtype != WINO_FP32X3) return fail(WINO_E_BADARG, "maxpool: bad dtype %d", dtype);
     if ((long long)n * c * (h / 2) * (w / 2) == 0) return WINO_OK;
     if (!in || !out) return fail(WINO_E_BADARG, "maxpool: NULL pointer");
     int rc = check_device();

@@ -47,6 +47,18 @@ __device__ __forceinline__ tf32_t from_float<tf32_t>(float v) {
     return t;
 }
 
+// Tag of the split operand format of the FP32X3 variant: a float x is stored as two TF32 values, head
+// hi = tf32(x) at column c and tail lo = tf32(x - hi) at column Cp + c of a row of 2*Cp floats.
+struct tf32x2_t {
+    float hi, lo;
+};
+__device__ __forceinline__ tf32x2_t split_tf32(float v) {
+    tf32x2_t r;
+    r.hi = from_float<tf32_t>(v).v;
+    r.lo = from_float<tf32_t>(v - r.hi).v;
+    return r;
+}
+
 // ---- layouts -----------------------------------------------------------------------------------------
 struct Strides {
     long long n, c, h, w;
@@ -71,7 +83,7 @@ __host__ __device__ inline Strides filter_strides(int layout, long long K, long 
 }
 
 // ---- geometry ----------------------------------------------------------------------------------------
-enum OperandKind { OP_F32 = 0, OP_TF32 = 1, OP_BF16 = 2, OP_F16 = 3 };
+enum OperandKind { OP_F32 = 0, OP_TF32 = 1, OP_BF16 = 2, OP_F16 = 3, OP_TF32X3 = 4 };
 
 struct Geometry {
     int m;            // output tile side (2 or 4)
@@ -80,7 +92,8 @@ struct Geometry {
     int ph, pw;       // stored output size (after optional pool)
     int bny, bnx;     // tiles per image
     int tiles_img;    // bny * bnx
-    int cp;           // V/U row length (channels padded, zero filled)
+    int cp;           // channels padded to 8 (zero filled): the contraction length of the tile GEMM
+    int crow;         // V/U row length in elements: cp, or 2*cp for the split operands of OP_TF32X3 (heads, then tails)
     int kq;           // M row length
     int operand;      // OperandKind of V and U
     int esize_io;     // bytes per activation element

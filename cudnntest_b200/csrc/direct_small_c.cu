@@ -473,7 +473,7 @@ int launch_direct_small_c_pack(const wino_conv_desc& d, const void* w, void* pac
     count_launch();
     if (d.dtype == WINO_BF16)
         pack_direct_filters<__nv_bfloat16><<<(total + 255) / 256, 256, 0, st>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)packed, d.k, d.c, sw);
-    else if (d.dtype == WINO_TF32)
+    else if (d.dtype == WINO_TF32)   // WINO_FP32 and WINO_FP32X3 both take the exact kernel below
         pack_direct_filters<float><<<(total + 255) / 256, 256, 0, st>>>((const float*)w, (float*)packed, d.k, d.c, sw);
     else        // exact FP32: the filters stay unrounded
         pack_direct_filters<float, true><<<(total + 255) / 256, 256, 0, st>>>((const float*)w, (float*)packed, d.k, d.c, sw);
@@ -496,7 +496,7 @@ int launch_direct_small_c(const wino_conv_desc& d, const Geometry& g, const void
     a.sw = filter_strides(d.layout_in, d.k, d.c);   // unused by the kernel: the filters arrive packed
     a.sy = act_strides(d.layout_out, d.n, d.k, g.oh, g.ow);
     if (a.pixels == 0) return WINO_OK;
-    if (d.dtype == WINO_FP32) {
+    if (d.dtype == WINO_FP32 || d.dtype == WINO_FP32X3) {
         const long long tiles = (a.pixels + 127) / 128;
         const long long max_ctas = 8LL * sm_count();
         dim3 grid((unsigned)(tiles < max_ctas ? tiles : max_ctas), (unsigned)((a.K + 63) / 64));

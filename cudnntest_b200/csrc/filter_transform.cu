@@ -5,6 +5,8 @@
 // One thread per (filter k, channel c); reads the nine taps through the filter layout's strides and
 // writes U[xi][k][Cp] with c fastest across the warp, zero filling c in [C, Cp).  HBM bound and tiny
 // (9 -> a*a values per (k, c)); meant to run once per weight tensor, not once per forward.
+#include <type_traits>
+
 #include "common.cuh"
 #include "wino_math.cuh"
 
@@ -32,11 +34,25 @@ __global__ void __launch_bounds__(256) filter_transform_kernel(const TIn* __rest
     }
     float t[A][A];
     filter_tile_transform<A>(g, t);
-    const long long plane = (long long)K * Cp;
+    if constexpr (std::is_same<TOp, tf32x2_t>::value) {
+        // split operands: rows of 2*Cp floats, the TF32 heads in [0, Cp), the TF32 tails in [Cp, 2*Cp)
+        float* uf = reinterpret_cast<float*>(u);
+        const long long plane = (long long)K * 2 * Cp, at = (long long)k * 2 * Cp + c;
 #pragma unroll
-    for (int i = 0; i < A; ++i)
+        for (int i = 0; i < A; ++i)
 #pragma unroll
-        for (int j = 0; j < A; ++j) u[(long long)(i * A + j) * plane + idx] = from_float<TOp>(t[i][j]);
+            for (int j = 0; j < A; ++j) {
+                const tf32x2_t sp = split_tf32(t[i][j]);
+                uf[(long long)(i * A + j) * plane + at] = sp.hi;
+                uf[(long long)(i * A + j) * plane + at + Cp] = sp.lo;
+            }
+    } else {
+        const long long plane = (long long)K * Cp;
+#pragma unroll
+        for (int i = 0; i < A; ++i)
+#pragma unroll
+            for (int j = 0; j < A; ++j) u[(long long)(i * A + j) * plane + idx] = from_float<TOp>(t[i][j]);
+    }
 }
 
 template <int A, typename TIn, typename TOp>
@@ -57,6 +73,7 @@ static int dispatch(const wino_conv_desc& d, const Geometry& g, const void* w, v
     switch (g.operand) {
         case OP_F32: return run<A, float, float>(d, g, w, u, st);
         case OP_TF32: return run<A, float, tf32_t>(d, g, w, u, st);
+        case OP_TF32X3: return run<A, float, tf32x2_t>(d, g, w, u, st);
         case OP_BF16: return run<A, __nv_bfloat16, __nv_bfloat16>(d, g, w, u, st);
         case OP_F16: return run<A, __nv_bfloat16, __half>(d, g, w, u, st);
     }

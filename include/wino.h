@@ -36,8 +36,12 @@ enum { WINO_NCHW = 0, WINO_NHWC = 1, WINO_CHWN = 2 };
 
 /* storage / arithmetic variants.  FP32: float storage, FP32 FFMA tile GEMM (the reference's
  * arithmetic).  TF32: float storage, tensor-core GEMM on TF32 operands.  BF16: bfloat16 storage,
- * tensor-core GEMM on BF16 or FP16 transform-domain operands.  Accumulation is always FP32. */
-enum { WINO_FP32 = 0, WINO_TF32 = 1, WINO_BF16 = 2 };
+ * tensor-core GEMM on BF16 or FP16 transform-domain operands.  FP32X3: float storage, tensor-core GEMM in which
+ * every transform-domain operand is split into a TF32 head and a TF32 tail (x = hi + lo) and each FP32 product is
+ * rebuilt from three TF32 products hi*hi + lo*hi + hi*lo (the dropped lo*lo term is below 2^-22 of the product):
+ * FP32-level accuracy (inside the 1e-4 bound of the FP32 variant, not bit-identical to it) at tensor-core speed.
+ * Accumulation is always FP32. */
+enum { WINO_FP32 = 0, WINO_TF32 = 1, WINO_BF16 = 2, WINO_FP32X3 = 3 };
 enum { WINO_OPERAND_AUTO = 0, WINO_OPERAND_BF16 = 1, WINO_OPERAND_F16 = 2 };
 
 enum {
@@ -52,7 +56,7 @@ enum {
 typedef struct wino_conv_desc {
     int layout_in, layout_out; /* WINO_NCHW / WINO_NHWC / WINO_CHWN; may differ (convLayoutTrans_*) */
     int n, c, h, w, k, pad;    /* batch, input channels, height, width, filters, zero padding        */
-    int dtype;                 /* WINO_FP32 / WINO_TF32 / WINO_BF16                                  */
+    int dtype;                 /* WINO_FP32 / WINO_TF32 / WINO_BF16 / WINO_FP32X3                    */
     int operand;               /* WINO_BF16 only: format of the transformed operands; AUTO = F16 (FP16
                                   operands keep both tile sizes inside the 5e-3 tolerance)          */
     int wino;                  /* output tile size m of F(m x m, 3x3): 2 or 4.  0 = the engine chooses:
