@@ -2,7 +2,7 @@
 """Benchmark of the hot path: the VGG-16 convolution stack (13 Winograd 3x3 convolutions with fused
 bias + ReLU, 2x2 max-pool fused at the five block ends) on synthetic data.
 
-    python bench.py --gpus N --steps K --warmup W [--dtype bf16|tf32|fp32] [--layout NHWC|NCHW|CHWN]
+    python bench.py --gpus N --steps K --warmup W [--dtype bf16|tf32|fp32|fp32x3] [--layout NHWC|NCHW|CHWN]
     python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...      (N > 1)
     python bench.py --impl reference ...        the CPU arm: the direct-convolution oracle on the host cores
 
@@ -33,7 +33,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--dtype", default="bf16", choices=["bf16", "tf32", "fp32"])
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "tf32", "fp32", "fp32x3"])
     ap.add_argument("--layout", default="NHWC", choices=["NHWC", "NCHW", "CHWN"])
     ap.add_argument("--batch", type=int, default=256, help="images per GPU per step")
     ap.add_argument("--wino", type=int, default=0, choices=[0, 2, 4])
@@ -325,7 +325,7 @@ def run_ours(args, rank, world, local_rank):
                "direct_tensor_core": 6}
     stage = {n: {"ms": float(stage_ms[i]), "launches": int(stage_n[i])} for n, i in classes.items()}
     dominant = max(classes, key=lambda n: stage[n]["ms"])
-    tpeak = peaks["tflops_sustained"] * (0.5 if args.dtype == "tf32" else 1.0)
+    tpeak = peaks["tflops_sustained"] * (0.5 if args.dtype in ("tf32", "fp32x3") else 1.0)
     byts, flops = model[dominant]["bytes"], model[dominant]["flops"]
     t_meas = stage[dominant]["ms"] * 1e-3
     t_hbm, t_tc = byts / (peaks["hbm_gbs"] * 1e9), flops / (tpeak * 1e12)
@@ -340,7 +340,7 @@ def run_ours(args, rank, world, local_rank):
         achieved = flops / t_meas / 1e12
         roofline = {"kernel": kernel_names[dominant], "bound": "tensor", "achieved": achieved, "peak": tpeak, "unit": "TFLOP/s",
                     "frac": achieved / tpeak, "traffic": None,
-                    "peak_source": peaks["source"] + " sustained bf16 cuBLAS" + (" halved for tf32" if args.dtype == "tf32" else "")}
+                    "peak_source": peaks["source"] + " sustained bf16 cuBLAS" + (" halved for tf32" if args.dtype in ("tf32", "fp32x3") else "")}
     if args.dtype == "fp32" and dominant == "tile_gemm_plain":
         roofline["note"] = ("the exact-FP32 tile GEMM is bound by the FP32 FMA pipe, which this object's hbm|tensor vocabulary does not "
                             "name: %.1f TFLOP/s of a nominal 74.4 (148 SMs x 128 lanes x 2 x 1.965 GHz)" % (flops / t_meas / 1e12))

@@ -6,15 +6,16 @@ direct-convolution-equivalent TFLOP/s, images/s and as a fraction of the rooflin
 The four configurations are the single-layer shapes the reference's harnesses are driven with
 (comparison/layoutCompare.cu:41-82 layers 6, 8, 9 and the 64 -> 64 case of layoutTest): all 3x3, stride 1, pad 1.
 
-  0  N=8,   C=K=64,  56x56, FP32, NCHW, no bias / ReLU
-  1  N=64,  C=K=256, 56x56, {FP32, TF32, BF16} x {NCHW, NHWC, CHWN}, bias + ReLU
-  2  N=64,  C=K=512, 28x28, {F(2x2,3x3), F(4x4,3x3)} x {BF16, FP32} x {NHWC, CHWN}
+  0  N=8,   C=K=64,  56x56, FP32 (and FP32X3), NCHW, no bias / ReLU
+  1  N=64,  C=K=256, 56x56, {FP32, FP32X3, TF32, BF16} x {NCHW, NHWC, CHWN}, bias + ReLU
+  2  N=64,  C=K=512, 28x28, {F(2x2,3x3), F(4x4,3x3)} x {BF16, FP32, FP32X3} x {NHWC, CHWN}
   3  N=128, C=K=512, 14x14, BF16, NCHW, bias + ReLU
 
 One JSON line per variant.  Figures: flops = 2 N K C H W 9 (direct-convolution equivalent); bytes = (x + w + y) in
 the storage type (+ 4 K for the bias); roofline time = max(bytes / HBM bandwidth, arithmetic / peak) where the
 arithmetic is what the chosen kernel really executes (the Winograd tile GEMM's 2 a^2 T C K, or the direct flops) and
-the peak is the measured BF16 tensor rate (half of it for TF32) or the nominal FP32 FFMA rate.  Inputs smaller than
+the peak is the measured BF16 tensor rate (half of it for TF32; FP32X3 executes three TF32 passes) or the nominal
+FP32 FFMA rate.  Inputs smaller than
 the L2 are evicted by rewriting a 256 MiB buffer before every timed call.
 """
 import argparse
@@ -28,11 +29,11 @@ from . import _lib
 from .conv import WinoConv, act_shape, device_status, filter_shape
 
 CONFIGS = {
-    0: dict(n=8, c=64, k=64, s=56, bias=False, relu=False, variants=[("fp32", "NCHW", 0)]),
+    0: dict(n=8, c=64, k=64, s=56, bias=False, relu=False, variants=[("fp32", "NCHW", 0), ("fp32x3", "NCHW", 0)]),
     1: dict(n=64, c=256, k=256, s=56, bias=True, relu=True,
-            variants=[(dt, lo, 0) for dt in ("fp32", "tf32", "bf16") for lo in ("NCHW", "NHWC", "CHWN")]),
+            variants=[(dt, lo, 0) for dt in ("fp32", "fp32x3", "tf32", "bf16") for lo in ("NCHW", "NHWC", "CHWN")]),
     2: dict(n=64, c=512, k=512, s=28, bias=False, relu=False,
-            variants=[(dt, lo, wino) for wino in (2, 4) for dt in ("bf16", "fp32") for lo in ("NHWC", "CHWN")]),
+            variants=[(dt, lo, wino) for wino in (2, 4) for dt in ("bf16", "fp32", "fp32x3") for lo in ("NHWC", "CHWN")]),
     3: dict(n=128, c=512, k=512, s=14, bias=True, relu=True, variants=[("bf16", "NCHW", 0)]),
 }
 
@@ -51,7 +52,7 @@ def load_peaks():
 
 def engine_runs_winograd(dtype, layout, n, c, k, s, wino):
     """Mirror of the library's per-layer choice for these shapes (C a multiple of 64, K a multiple of 16)."""
-    if wino or dtype == "fp32":
+    if wino or dtype in ("fp32", "fp32x3"):
         return True
     if dtype == "bf16":
         return not (c <= 256 or s * s < 28 * 28 or n * s * s < 128 * 28 * 28)
@@ -90,7 +91,10 @@ def run_variant(cfg_id, cfg, dtype, layout, wino, iters, peaks, flush):
     winograd = engine_runs_winograd(dtype, layout, n, c, k, s, wino)
     m = wino or 4
     arithmetic = 2.0 * (m + 2) ** 2 * n * math.ceil(s / m) ** 2 * c * k if winograd else flops
-    peak = {"bf16": peaks["bf16_tflops"], "tf32": peaks["bf16_tflops"] / 2, "fp32": FFMA_TFLOPS_NOMINAL}[dtype]
+    if dtype == "fp32x3":
+        arithmetic *= 3     # three TF32 products rebuild one FP32 product
+    peak = {"bf16": peaks["bf16_tflops"], "tf32": peaks["bf16_tflops"] / 2, "fp32x3": peaks["bf16_tflops"] / 2,
+            "fp32": FFMA_TFLOPS_NOMINAL}[dtype]
     t_hbm, t_math = byts / (peaks["hbm_gbs"] * 1e9), arithmetic / (peak * 1e12)
     roof_ms = max(t_hbm, t_math) * 1e3
     return {"config": cfg_id, "n": n, "c": c, "k": k, "h": s, "dtype": dtype, "layout": layout,

@@ -6,7 +6,7 @@
 //   opt 0/1/2  this library, NCHW / NHWC / CHWN
 //   opt 3..6   cuDNN WINOGRAD_NONFUSED / WINOGRAD in NCHW, then in NHWC (FP32, FMA math), as in the reference
 //   opt 7/8    cuDNN's fastest forward algorithm in NCHW / NHWC for the chosen dtype ("cuDNN best")
-// Additions: dtype=fp32|tf32|bf16 (default fp32, the reference's arithmetic), wino=4|2|0 (0 = the engine's choice of
+// Additions: dtype=fp32|fp32x3|tf32|bf16 (default fp32, the reference's arithmetic; fp32x3 = split-TF32 tensor-core GEMM), wino=4|2|0 (0 = the engine's choice of
 // kernel per layer, the default for tf32 / bf16; 4 = F(4x4,3x3) Winograd, the default for fp32), seed=, check=0|1,
 // iters=.  With dtype=fp32 and opt 0..2 the timed call is layoutManager() through include/wino_compat.cuh, i.e.
 // the reference's own call with its semantics (filter transform inside, synchronous); a second figure times
@@ -33,7 +33,8 @@ int main(int argc, char** argv) {
     const int check = (int)arg_int(argc, argv, "check", 1);
     const uint64_t seed = (uint64_t)arg_int(argc, argv, "seed", 0xC0DE);
     const std::string dts = arg_str(argc, argv, "dtype", "fp32");
-    const int dtype = dts == "bf16" ? WINO_BF16 : dts == "tf32" ? WINO_TF32 : WINO_FP32;
+    const int dtype = dts == "bf16" ? WINO_BF16 : dts == "tf32" ? WINO_TF32 : dts == "fp32x3" ? WINO_FP32X3 : WINO_FP32;
+    const int cudnn_dtype = dtype == WINO_FP32X3 ? WINO_FP32 : dtype;   // FP32-accurate variants face cuDNN's CUDNN_FMA_MATH
     const int device = (int)arg_int(argc, argv, "device", 0);   // the reference hard-codes device 1 (layoutCompare.cu:33)
     LayerShape ls;
     if (!vgg_layer(layer, &ls) || opt < 0 || opt > 8) {
@@ -140,7 +141,7 @@ int main(int argc, char** argv) {
         cudnnHandle_t handle;
         HCHECK_CUDNN(cudnnCreate(&handle));
         if (opt <= 6) {
-            if (dtype != WINO_FP32) { fprintf(stderr, "opt 3..6 are the reference's FP32 cuDNN modes; use opt 7/8 for %s\n", dts.c_str()); return 1; }
+            if (cudnn_dtype != WINO_FP32) { fprintf(stderr, "opt 3..6 are the reference's FP32 cuDNN modes; use opt 7/8 for %s\n", dts.c_str()); return 1; }
             cudnnTensorDescriptor_t xdesc, ydesc;
             cudnnFilterDescriptor_t wdesc;
             cudnnConvolutionDescriptor_t cdesc;
@@ -164,7 +165,7 @@ int main(int argc, char** argv) {
             }
             note = "cuDNN legacy algorithm, FMA math";
         } else {
-            const CudnnBest b = cudnn_best_forward(handle, opt == 7 ? CUDNN_TENSOR_NCHW : CUDNN_TENSOR_NHWC, dtype, n, c, h, h, k, pad, xd, wd, yd, 5, iters);
+            const CudnnBest b = cudnn_best_forward(handle, opt == 7 ? CUDNN_TENSOR_NCHW : CUDNN_TENSOR_NHWC, cudnn_dtype, n, c, h, h, k, pad, xd, wd, yd, 5, iters);
             if (b.ms < 0) { printf("{\"opt\": %d, \"layer\": %d, \"unsupported\": true, \"tried\": \"%s\"}\n", opt, layer, b.tried.c_str()); return 0; }
             times.assign(iters, (float)b.ms);
             note = std::string("cuDNN best = ") + fwd_algo_name(b.algo) + " of [" + b.tried + "]";
@@ -194,7 +195,7 @@ int main(int argc, char** argv) {
     double err = -1;
     if (check) {
         err = spot_check(layout, layout, n, c, h, h, k, pad, x.data(), w.data(), nullptr, false, y.data(), 2000, seed + 7);
-        const double tol = dtype == WINO_FP32 ? 1e-4 : 2e-2;   // max-norm of sampled outputs; the L2 bars live in the test-suite
+        const double tol = cudnn_dtype == WINO_FP32 ? 1e-4 : 2e-2;   // max-norm of sampled outputs; the L2 bars live in the test-suite
         if (!(err <= tol)) printf("moduleConv error\n");
     }
     printf("{\"harness\": \"layoutCompare\", \"opt\": %d, \"layer\": %d, \"batch\": %d, \"layout\": \"%s\", \"dtype\": \"%s\", \"c\": %d, "

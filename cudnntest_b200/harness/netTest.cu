@@ -8,7 +8,7 @@
 //                (layoutManager + addBias + relu (+ pool), Network.h:456-519, :603-669)
 //   mode 3/4     cuDNN in NCHW / NHWC: fastest forward algorithm per layer + cudnnAddTensor +
 //                cudnnActivationForward (+ cudnnPoolingForward), i.e. Network.h:171-312, :314-444
-// plus dtype=fp32|tf32|bf16 (default bf16), rounds= (default 10), tail=0|1.  With tail=1 the classifier tail of the
+// plus dtype=fp32|fp32x3|tf32|bf16 (default bf16), rounds= (default 10), tail=0|1.  With tail=1 the classifier tail of the
 // reference (fc14 + ReLU, fc15 + ReLU, fc16, softmax, arg-max: Network.h:668-704) runs after the last round on the
 // output of conv13 (classifier_tail.h: cuBLAS GEMMs + small kernels), is checked against a host restatement for two
 // images and reports the top-1 classes.  The pretrained weights (./vggData/*.bin) and ImageNet batches the reference
@@ -33,7 +33,8 @@ int main(int argc, char** argv) {
     const int rounds = (int)arg_int(argc, argv, "rounds", 10);
     const int tail = (int)arg_int(argc, argv, "tail", 0);
     const std::string dts = arg_str(argc, argv, "dtype", "bf16");
-    const int dtype = dts == "bf16" ? WINO_BF16 : dts == "tf32" ? WINO_TF32 : WINO_FP32;
+    const int dtype = dts == "bf16" ? WINO_BF16 : dts == "tf32" ? WINO_TF32 : dts == "fp32x3" ? WINO_FP32X3 : WINO_FP32;
+    const int cudnn_dtype = dtype == WINO_FP32X3 ? WINO_FP32 : dtype;   // FP32-accurate variants face cuDNN's CUDNN_FMA_MATH
     HCHECK_CUDA(cudaSetDevice((int)arg_int(argc, argv, "device", 0)));
     if (mode < 0 || mode > 4 || n <= 0) { fprintf(stderr, "mode must be 0..4, batch positive\n"); return 1; }
     const int layout = mode <= 2 ? mode : mode == 3 ? WINO_NCHW : WINO_NHWC;
@@ -128,7 +129,7 @@ int main(int argc, char** argv) {
             for (int p = 0; p < l; ++p)
                 if (kVgg[p].c == kVgg[l].c && kVgg[p].k == kVgg[l].k && kVgg[p].s == kVgg[l].s) algo[l] = algo[p];
             if (algo[l] < 0) {
-                const CudnnBest b = cudnn_best_forward(handle, fmt, dtype, n, kVgg[l].c, kVgg[l].s, kVgg[l].s, kVgg[l].k, 1,
+                const CudnnBest b = cudnn_best_forward(handle, fmt, cudnn_dtype, n, kVgg[l].c, kVgg[l].s, kVgg[l].s, kVgg[l].k, 1,
                                                        l == 0 ? input : act[0], wdev[l], act[1], 2, 5);
                 if (b.algo < 0) { printf("{\"harness\": \"netTest\", \"mode\": %d, \"unsupported\": \"layer %d: %s\"}\n", mode, l + 1, b.tried.c_str()); return 0; }
                 algo[l] = b.algo;
@@ -150,7 +151,7 @@ int main(int argc, char** argv) {
         HCHECK_CUDNN(cudnnSetActivationDescriptor(ad, CUDNN_ACTIVATION_RELU, CUDNN_PROPAGATE_NAN, 0.0));
         HCHECK_CUDNN(cudnnSetPooling2dDescriptor(pool, CUDNN_POOLING_MAX, CUDNN_PROPAGATE_NAN, 2, 2, 0, 0, 2, 2));
         HCHECK_CUDNN(cudnnSetConvolution2dDescriptor(cd, 1, 1, 1, 1, 1, 1, CUDNN_CROSS_CORRELATION, CUDNN_DATA_FLOAT));
-        HCHECK_CUDNN(cudnnSetConvolutionMathType(cd, dtype == WINO_FP32 ? CUDNN_FMA_MATH : CUDNN_TENSOR_OP_MATH_ALLOW_CONVERSION));
+        HCHECK_CUDNN(cudnnSetConvolutionMathType(cd, cudnn_dtype == WINO_FP32 ? CUDNN_FMA_MATH : CUDNN_TENSOR_OP_MATH_ALLOW_CONVERSION));
         void* bias_t[13];   // biases in the tensor data type, as cudnnAddTensor wants
         for (int l = 0; l < 13; ++l) {
             bias_t[l] = bdev[l];

@@ -9,7 +9,7 @@
 // points of the C ABI, so a change to one kernel (tile shape, F(2x2) against F(4x4), operand format) shows up in
 // its own column and in the weighted sum.
 //
-//   stageBench batch=B layout=nchw|nhwc|chwn dtype=fp32|tf32|bf16 wino=4|2 iters=20 hbm=<GB/s> tflops=<TFLOP/s>
+//   stageBench batch=B layout=nchw|nhwc|chwn dtype=fp32|fp32x3|tf32|bf16 wino=4|2 iters=20 hbm=<GB/s> tflops=<TFLOP/s>
 //
 // Per case it prints one line per stage: avg / min / max microseconds, algorithmic GB/s (or TFLOP/s for the GEMM) and
 // the fraction of the peak given on the command line (defaults: the HBM copy bandwidth and the sustained BF16 GEMM
@@ -59,7 +59,7 @@ int main(int argc, char** argv) {
     const int iters = (int)arg_int(argc, argv, "iters", 20);
     const int wino = (int)arg_int(argc, argv, "wino", 4);
     const std::string dts = arg_str(argc, argv, "dtype", "bf16"), los = arg_str(argc, argv, "layout", "nhwc");
-    const int dtype = dts == "bf16" ? WINO_BF16 : dts == "tf32" ? WINO_TF32 : WINO_FP32;
+    const int dtype = dts == "bf16" ? WINO_BF16 : dts == "tf32" ? WINO_TF32 : dts == "fp32x3" ? WINO_FP32X3 : WINO_FP32;
     const int layout = los == "nchw" ? WINO_NCHW : los == "chwn" ? WINO_CHWN : WINO_NHWC;
     const double hbm = atof(arg_str(argc, argv, "hbm", "6538.6").c_str());
     const double tpeak = atof(arg_str(argc, argv, "tflops", "1351.9").c_str());
@@ -106,7 +106,7 @@ int main(int argc, char** argv) {
         const long long tp = wino_stage_tile_rows(&d, n);
         const int cp = wino_stage_cp(&d), kq = wino_stage_kq(&d);
         if (tp <= 0 || cp <= 0 || kq <= 0) { fprintf(stderr, "libwino: %s\n", wino_last_error_string()); return 3; }
-        const bool fused = dtype != WINO_FP32;               // tensor-core variants have the row-fused pair of stages
+        const bool fused = dtype == WINO_TF32 || dtype == WINO_BF16;              // tensor-core variants have the row-fused pair of stages
         const size_t op_es = dtype == WINO_BF16 ? 2 : 4;
         const size_t v_bytes = (size_t)a * a * tp * cp * op_es;
         const size_t m_bytes = (size_t)a * a * tp * kq * 4;  // large enough for the raw products and for Z
@@ -129,7 +129,7 @@ int main(int argc, char** argv) {
             HCHECK_CUDA(cudaMemcpy(y.data(), yd, ny * 4, cudaMemcpyDeviceToHost));
         }
         const double err = spot_check(layout, layout, n, c, h, h, k, pad, x.data(), w.data(), bias.data(), true, y.data(), 500, 77 + ci);
-        const bool valid = err <= (dtype == WINO_FP32 ? 1e-4 : 2e-2);
+        const bool valid = err <= (dtype == WINO_FP32 || dtype == WINO_FP32X3 ? 1e-4 : 2e-2);
         all_valid = all_valid && valid;
         Timing t_gz, t_oz;
         if (fused) {
@@ -158,7 +158,7 @@ int main(int argc, char** argv) {
         // algorithmic bytes / flops of each stage (unpadded tile count T)
         const long long bn = (h + wino - 1) / wino;
         const double T = (double)n * bn * bn;
-        const double b_in = (double)n * c * h * h * es + (double)a * a * T * c * op_es;
+        const double b_in = (double)n * c * h * h * es + (double)a * a * T * c * op_es * (dtype == WINO_FP32X3 ? 2 : 1);
         const double f_g = 2.0 * a * a * T * c * k;
         const double b_out = (double)a * a * T * k * 4 + (double)n * k * h * h * es;
         const double b_oz = (double)a * wino * T * k * (dtype == WINO_BF16 ? 2 : 4) + (double)n * k * h * h * es;

@@ -69,13 +69,14 @@ def kernel_model(batch, dtype="bf16", wino=4, layers=VGG16_CONV, layout="NHWC", 
             continue
         tiles = batch * math.ceil(s / m) ** 2
         cp, kq = math.ceil(c / 8) * 8, math.ceil(k / 8) * 8
-        v_bytes = a * a * tiles * cp * s_io
-        fused = dtype != "fp32" and c <= 128
+        split = dtype == "fp32x3"      # operands kept as TF32 head + tail: V rows twice as long, three TF32 passes
+        v_bytes = a * a * tiles * cp * s_io * (2 if split else 1)
+        fused = dtype in ("tf32", "bf16") and c <= 128
         p_bytes = (a * m * tiles * kq * (2 if dtype == "bf16" else 4)) if fused else a * a * tiles * kq * 4
         out["input_transform"]["bytes"] += batch * c * s * s * s_io + v_bytes
         g = out["tile_gemm_rowfused" if fused else "tile_gemm_plain"]
         g["bytes"] += v_bytes + p_bytes
-        g["flops"] += 2 * a * a * tiles * c * k
+        g["flops"] += 2 * a * a * tiles * c * k * (3 if split else 1)     # executed tensor-core flops
         out["output_transform"]["bytes"] += p_bytes + batch * k * o * o * s_io
     return out
 
