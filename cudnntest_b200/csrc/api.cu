@@ -135,7 +135,7 @@ static long long slab_budget_bytes() {
 }
 
 long long per_image_bytes(const Geometry& g) {
-    return (long long)g.tiles_img * ((long long)g.a * g.a * g.crow * g.esize_op + (long long)g.prod_planes * g.kq * g.esize_prod);
+    return (long long)g.tiles_img * ((long long)g.a * g.a * g.cp * g.esize_op + (long long)g.prod_planes * g.kq * g.esize_prod);
 }
 
 // images per slab
@@ -151,7 +151,7 @@ static int slab_images(const wino_conv_desc& d, const Geometry& g) {
 long long tile_rows(const Geometry& g, int ns) { return round_up_ll((long long)ns * g.tiles_img, 128); }
 
 size_t v_bytes(const Geometry& g, long long tp) {
-    return (size_t)round_up_ll((long long)g.a * g.a * tp * g.crow * g.esize_op, 1024);
+    return (size_t)round_up_ll((long long)g.a * g.a * tp * g.cp * g.esize_op, 1024);
 }
 size_t m_bytes(const Geometry& g, long long tp) {
     return (size_t)round_up_ll((long long)g.a * g.a * tp * g.kq * 4, 1024);
@@ -165,6 +165,8 @@ int run_gemm(const Geometry& g, const void* v, const void* u, float* m, int k, l
                     cudaStream_t st) {
     if (g.operand == OP_F32)
         return launch_gemm_ffma((const float*)v, (const float*)u, m, g.a * g.a, t_rows, tp, k, g.cp, g.kq, st);
+    if (g.operand == OP_TF32X3)
+        return launch_gemm_tc_split((const float*)v, (const float*)u, m, g.a * g.a, t_rows, tp, k, g.cp, g.kq, st);
     return launch_gemm_tc(g.operand, v, u, m, g.a * g.a, t_rows, tp, k, g.cp, g.kq, st);
 }
 
@@ -268,7 +270,7 @@ long long wino_stage_tile_rows(const wino_conv_desc* d, int ns) {
 int wino_stage_cp(const wino_conv_desc* d) {
     Geometry g;
     if (make_geometry(d, &g) != WINO_OK) return -1;
-    return g.crow;
+    return g.cp;
 }
 
 int wino_stage_kq(const wino_conv_desc* d) {

@@ -47,8 +47,9 @@ __device__ __forceinline__ tf32_t from_float<tf32_t>(float v) {
     return t;
 }
 
-// Tag of the split operand format of the FP32X3 variant: a float x is stored as two TF32 values, head
-// hi = tf32(x) at column c and tail lo = tf32(x - hi) at column Cp + c of a row of 2*Cp floats.
+// Split operand of the FP32X3 variant: a float x is used as two TF32 values, head hi = tf32(x) and tail
+// lo = tf32(x - hi).  The transformed filters are stored that way (head at column c, tail at column Cp + c of a row
+// of 2*Cp floats); the transformed input tiles are split inside the tile GEMM.
 struct tf32x2_t {
     float hi, lo;
 };
@@ -93,7 +94,7 @@ struct Geometry {
     int bny, bnx;     // tiles per image
     int tiles_img;    // bny * bnx
     int cp;           // channels padded to 8 (zero filled): the contraction length of the tile GEMM
-    int crow;         // V/U row length in elements: cp, or 2*cp for the split operands of OP_TF32X3 (heads, then tails)
+    int crow;         // U row length in elements: cp, or 2*cp for OP_TF32X3 (cp TF32 heads, then cp TF32 tails); V rows are always cp
     int kq;           // M row length
     int operand;      // OperandKind of V and U
     int esize_io;     // bytes per activation element

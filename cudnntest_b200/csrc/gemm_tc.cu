@@ -42,7 +42,6 @@ struct TcParams {
     long long t_rows;
     int kq, cp;
     int batches, mblocks, nblocks, kchunks;
-    int part_chunks;   // 0, or ring slots per term of the split-operand (3 x TF32) contraction: kchunks = 3 * part_chunks
     uint32_t idesc;
     int* status;
 };
@@ -110,18 +109,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant__
                 const int xi = (int)(tile / ((long long)p.nblocks * p.mblocks));
                 for (int kc = 0; kc < p.kchunks; ++kc) {
                     if (!mbar_wait_warp(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, TC_WAIT_EMPTY)) { ok = false; break; }
-                    // split operands: rows hold Cp heads then Cp tails; the three terms run smallest first,
-                    // tail(V) x head(U), head(V) x tail(U), head(V) x head(U)
-                    int cv = kc * KC, cu = kc * KC;
-                    if (p.part_chunks) {
-                        const int term = kc / p.part_chunks, j = kc - term * p.part_chunks;
-                        cv = j * KC + (term == 0 ? p.cp : 0);
-                        cu = j * KC + (term == 1 ? p.cp : 0);
-                    }
                     if (issuer) {
                         mbar_arrive_expect_tx(bar_full + 8 * stage, TC_A_BYTES + L::B_BYTES);
-                        tma_load_3d(a_ring + stage * TC_A_BYTES, &tm_v, bar_full + 8 * stage, cv, mb * TC_BM, xi);
-                        tma_load_3d(b_ring + stage * L::B_BYTES, &tm_u, bar_full + 8 * stage, cu, nb * BN, xi);
+                        tma_load_3d(a_ring + stage * TC_A_BYTES, &tm_v, bar_full + 8 * stage, kc * KC, mb * TC_BM, xi);
+                        tma_load_3d(b_ring + stage * L::B_BYTES, &tm_u, bar_full + 8 * stage, kc * KC, nb * BN, xi);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -141,8 +132,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant__
                 for (int kc = 0; kc < p.kchunks; ++kc) {
                     if (!mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, p.status, TC_WAIT_FULL)) { ok = false; break; }
                     tc_fence_after();
-                    // a term's last slot may reach past its Cp columns (into the other half of the row): not multiplied
-                    const int left = p.cp - (p.part_chunks ? kc % p.part_chunks : kc) * KC;
+                    const int left = p.cp - kc * KC;
                     const int ksteps = left >= KC ? KC / UMMA_K : (left + UMMA_K - 1) / UMMA_K;
                     // descriptors once per ring slot; a K-step adds 32 bytes = 2 sixteen-byte units to the start address
                     const uint64_t a_desc = smem_desc_k128(a_ring + stage * TC_A_BYTES), b_desc = smem_desc_k128(b_ring + stage * L::B_BYTES);
@@ -245,29 +235,24 @@ int run(const CUtensorMap& tm_v, const CUtensorMap& tm_u, const CUtensorMap& tm_
 int launch_gemm_tc(int operand, const void* v, const void* u, float* m, int batches, long long t_rows, long long tp,
                    int k, int cp, int kq, cudaStream_t st) {
     if (t_rows <= 0) return WINO_OK;
-    if (operand != OP_TF32 && operand != OP_BF16 && operand != OP_F16 && operand != OP_TF32X3)
+    if (operand != OP_TF32 && operand != OP_BF16 && operand != OP_F16)
         return fail(WINO_E_BADARG, "gemm_tc: bad operand kind %d", operand);
-    const bool split = operand == OP_TF32X3;   // rows of 2*cp floats: heads, then tails
-    if (split) operand = OP_TF32;
-    const int crow = split ? 2 * cp : cp;
     const int es = operand == OP_TF32 ? 4 : 2;
     if ((cp * es) % 16 != 0 || kq % 4 != 0) return fail(WINO_E_BADARG, "gemm_tc: row pitch must be a multiple of 16 bytes");
     if (((uintptr_t)v | (uintptr_t)u | (uintptr_t)m) & 15) return fail(WINO_E_BADARG, "gemm_tc: buffers must be 16-byte aligned");
     static const int force_bn = [] { const char* e = getenv("WINO_GEMM_BN"); return e ? atoi(e) : 0; }();
-    const int bn = force_bn ? force_bn : k <= 64 ? 64 : (k >= 256 && (split ? 3 * cp : cp) >= 512) ? 256 : 128;   // long contractions: wider tiles, fewer passes over V
+    const int bn = force_bn ? force_bn : k <= 64 ? 64 : (k >= 256 && cp >= 512) ? 256 : 128;   // long contractions: wider tiles, fewer passes over V
     const CUtensorMapDataType dt = operand_map_type(operand);
     CUtensorMap tm_v, tm_u, tm_m;
     int rc;
-    if ((rc = make_map_k128(&tm_v, dt, es, v, crow, t_rows, tp, batches, TC_BM))) return rc;
-    if ((rc = make_map_k128(&tm_u, dt, es, u, crow, k, k, batches, bn))) return rc;
+    if ((rc = make_map_k128(&tm_v, dt, es, v, cp, t_rows, tp, batches, TC_BM))) return rc;
+    if ((rc = make_map_k128(&tm_u, dt, es, u, cp, k, k, batches, bn))) return rc;
     if ((rc = make_map_k128(&tm_m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, m, kq, t_rows, tp, batches, 32))) return rc;
     TcParams p;
     p.t_rows = t_rows; p.cp = cp; p.kq = kq; p.batches = batches;
     p.mblocks = (int)((t_rows + TC_BM - 1) / TC_BM);
     p.nblocks = (k + bn - 1) / bn;
     p.kchunks = (cp * es + TC_ROW_BYTES - 1) / TC_ROW_BYTES;
-    p.part_chunks = split ? p.kchunks : 0;
-    if (split) p.kchunks *= 3;
     p.idesc = make_idesc(operand, bn);
     if ((rc = status_word(&p.status))) return rc;
     const bool tf32 = operand == OP_TF32;

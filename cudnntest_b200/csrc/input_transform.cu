@@ -20,7 +20,6 @@
 // HBM bound: reads N*C*H*W elements (x ~1.5 through L2 for the vertical halo), writes a*a*T*Cp.
 #include <cstdlib>
 #include <mutex>
-#include <type_traits>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -34,8 +33,7 @@ struct ITArgs {
     int C, H, W, pad;
     int n0, ns;
     int bny, bnx;
-    int cp;      // channels padded to 8
-    int crow;    // elements per V row: cp, or 2*cp for split operands (cp heads, then cp tails)
+    int cp;
     long long tp;
     Strides sx;
 };
@@ -53,12 +51,6 @@ struct WordIO<float, TOp> {          // one float channel per word
     static __device__ __forceinline__ uint32_t put(float a, float) {
         return __float_as_uint(to_float<TOp>(from_float<TOp>(a)));
     }
-};
-template <>
-struct WordIO<float, tf32x2_t> {     // one float channel per word in, two words out (see transform_words)
-    static constexpr int VEC = 1;
-    static __device__ __forceinline__ float get(uint32_t w, int) { return __uint_as_float(w); }
-    static __device__ __forceinline__ uint32_t put(float a, float) { return __float_as_uint(split_tf32(a).hi); }
 };
 template <>
 struct WordIO<__nv_bfloat16, __nv_bfloat16> {
@@ -82,10 +74,9 @@ struct WordIO<__nv_bfloat16, __half> {
 // Transforms the a x a patch whose words sit at src[(r*row_stride + s*col_stride) * 32] and stores the a*a
 // results as words at dst[xi * plane_words].
 // SWZ: the word of lane l for patch element (r, q) sits at column l ^ (r*A + q) of its row (CHWN staging).
-// Split operands (TOp = tf32x2_t): the TF32 head goes to dst, the TF32 tail `tail_off` words further along the row.
 template <int A, typename TIn, typename TOp, bool SWZ = false>
 __device__ __forceinline__ void transform_words(const uint32_t* src, int row_stride, int col_stride, uint32_t* dst,
-                                                long long plane_words, int lane = 0, int tail_off = 0) {
+                                                long long plane_words, int lane = 0) {
     using IO = WordIO<TIn, TOp>;
     uint32_t w[A][A];
 #pragma unroll
@@ -109,15 +100,7 @@ __device__ __forceinline__ void transform_words(const uint32_t* src, int row_str
 #pragma unroll
     for (int r = 0; r < A; ++r)
 #pragma unroll
-        for (int q = 0; q < A; ++q) {
-            if constexpr (std::is_same<TOp, tf32x2_t>::value) {
-                const tf32x2_t sp = split_tf32(lo[r][q]);
-                dst[(long long)(r * A + q) * plane_words] = __float_as_uint(sp.hi);
-                dst[(long long)(r * A + q) * plane_words + tail_off] = __float_as_uint(sp.lo);
-            } else {
-                dst[(long long)(r * A + q) * plane_words] = IO::put(lo[r][q], IO::VEC == 2 ? hi[r][q] : 0.f);
-            }
-        }
+        for (int q = 0; q < A; ++q) dst[(long long)(r * A + q) * plane_words] = IO::put(lo[r][q], IO::VEC == 2 ? hi[r][q] : 0.f);
 }
 
 // writes element (channel c_l of the unit) of spatial position `pos` into the staged word rows
@@ -190,7 +173,7 @@ __global__ void __launch_bounds__(256, 2) input_transform_strip(const ITArgs a, 
     if (bx < a.bnx && c < a.cp) {
         const long long t = ((long long)blockIdx.z * a.bny + by) * a.bnx + bx;
         transform_words<A, TIn, TOp>(reinterpret_cast<const uint32_t*>(patch) + (tl * M) * 32 + lane, COLS, 1,
-                                     reinterpret_cast<uint32_t*>(a.v) + (t * a.crow + c) / VEC, a.tp * a.crow / VEC, 0, a.cp);
+                                     reinterpret_cast<uint32_t*>(a.v) + (t * a.cp + c) / VEC, a.tp * a.cp / VEC);
     }
 }
 
@@ -242,7 +225,7 @@ __global__ void __launch_bounds__(256, 2) input_transform_batch(const ITArgs a, 
     if (nb0 + n_l < a.ns && c < a.cp) {
         const long long t = ((long long)(nb0 + n_l) * a.bny + by) * a.bnx + bx;
         transform_words<A, TIn, TOp, true>(reinterpret_cast<const uint32_t*>(patch) + n_l * 32, A * IT_NB, IT_NB,
-                                           reinterpret_cast<uint32_t*>(a.v) + (t * a.crow + c) / VEC, a.tp * a.crow / VEC, lane, a.cp);
+                                           reinterpret_cast<uint32_t*>(a.v) + (t * a.cp + c) / VEC, a.tp * a.cp / VEC, lane);
     }
 }
 
@@ -291,7 +274,7 @@ input_transform_nhwc_tma(const __grid_constant__ CUtensorMap tm_x, const ITArgs 
         for (long long i = 0; i < n_my && i < ITT_STAGES - 1; ++i) issue(i);
 
     const int tl = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const long long plane_words = a.tp * a.crow / VEC;
+    const long long plane_words = a.tp * a.cp / VEC;
     uint32_t* __restrict__ vw = reinterpret_cast<uint32_t*>(a.v);
     bool aborted = false;
     for (long long i = 0; i < n_my; ++i) {
@@ -305,7 +288,7 @@ input_transform_nhwc_tma(const __grid_constant__ CUtensorMap tm_x, const ITArgs 
         if (bx < a.bnx && c < a.cp) {
             const long long t = ((long long)n_l * a.bny + by) * a.bnx + bx;
             transform_words<A, TIn, TOp>(reinterpret_cast<const uint32_t*>(smem + s * STAGE_BYTES) + (tl * M) * 32 + lane, COLS, 1,
-                                         vw + (t * a.crow + c) / VEC, plane_words, 0, a.cp);
+                                         vw + (t * a.cp + c) / VEC, plane_words);
         }
         __syncthreads();   // the slot is free for the load issued at the top of the next iteration
     }
@@ -384,7 +367,7 @@ static int dispatch(const wino_conv_desc& d, const Geometry& g, const ITArgs& a,
     switch (g.operand) {
         case OP_F32: return run<A, float, float>(d, g, a, st);
         case OP_TF32: return run<A, float, tf32_t>(d, g, a, st);
-        case OP_TF32X3: return run<A, float, tf32x2_t>(d, g, a, st);
+        case OP_TF32X3: return run<A, float, float>(d, g, a, st);   // plain FP32 V: the tile GEMM splits it
         case OP_BF16: return run<A, __nv_bfloat16, __nv_bfloat16>(d, g, a, st);
         case OP_F16: return run<A, __nv_bfloat16, __half>(d, g, a, st);
     }
@@ -399,7 +382,7 @@ int launch_input_transform(const wino_conv_desc& d, const Geometry& g, const voi
                     g.bny, g.bnx);
     ITArgs a;
     a.x = x; a.v = v; a.C = d.c; a.H = d.h; a.W = d.w; a.pad = d.pad;
-    a.n0 = n0; a.ns = ns; a.bny = g.bny; a.bnx = g.bnx; a.cp = g.cp; a.crow = g.crow; a.tp = tp;
+    a.n0 = n0; a.ns = ns; a.bny = g.bny; a.bnx = g.bnx; a.cp = g.cp; a.tp = tp;
     a.sx = act_strides(d.layout_in, d.n, d.c, d.h, d.w);
     return g.a == 6 ? dispatch<6>(d, g, a, st) : dispatch<4>(d, g, a, st);
 }

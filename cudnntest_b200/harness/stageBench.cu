@@ -158,7 +158,7 @@ int main(int argc, char** argv) {
         // algorithmic bytes / flops of each stage (unpadded tile count T)
         const long long bn = (h + wino - 1) / wino;
         const double T = (double)n * bn * bn;
-        const double b_in = (double)n * c * h * h * es + (double)a * a * T * c * op_es * (dtype == WINO_FP32X3 ? 2 : 1);
+        const double b_in = (double)n * c * h * h * es + (double)a * a * T * c * op_es;
         const double f_g = 2.0 * a * a * T * c * k;
         const double b_out = (double)a * a * T * k * 4 + (double)n * k * h * h * es;
         const double b_oz = (double)a * wino * T * k * (dtype == WINO_BF16 ? 2 : 4) + (double)n * k * h * h * es;

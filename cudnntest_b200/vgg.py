@@ -69,8 +69,8 @@ def kernel_model(batch, dtype="bf16", wino=4, layers=VGG16_CONV, layout="NHWC", 
             continue
         tiles = batch * math.ceil(s / m) ** 2
         cp, kq = math.ceil(c / 8) * 8, math.ceil(k / 8) * 8
-        split = dtype == "fp32x3"      # operands kept as TF32 head + tail: V rows twice as long, three TF32 passes
-        v_bytes = a * a * tiles * cp * s_io * (2 if split else 1)
+        split = dtype == "fp32x3"      # V stays plain FP32 and is split into TF32 head + tail inside the tile GEMM
+        v_bytes = a * a * tiles * cp * s_io
         fused = dtype in ("tf32", "bf16") and c <= 128
         p_bytes = (a * m * tiles * kq * (2 if dtype == "bf16" else 4)) if fused else a * a * tiles * kq * 4
         out["input_transform"]["bytes"] += batch * c * s * s * s_io + v_bytes
