@@ -145,6 +145,8 @@ static int slab_images(const wino_conv_desc& d, const Geometry& g) {
     if (ns < 1) ns = 1;
     if (ns > d.n) ns = d.n;
     if (ns > 65535) ns = 65535;
+    // several slabs: start each on a multiple of 8 images, so that the CHWN kernels keep their 16-byte vectors along n
+    if (ns < d.n && ns >= 8 && d.slab_images <= 0) ns -= ns % 8;
     return (int)ns;
 }
 
