@@ -329,7 +329,7 @@ def run_ours(args, rank, world, local_rank):
     byts, flops = model[dominant]["bytes"], model[dominant]["flops"]
     t_meas = stage[dominant]["ms"] * 1e-3
     t_hbm, t_tc = byts / (peaks["hbm_gbs"] * 1e9), flops / (tpeak * 1e12)
-    kernel_names = {"input_transform": "input_transform_nhwc_tma", "tile_gemm_plain": "gemm_tc_kernel" if args.dtype != "fp32" else "gemm_ffma_kernel",
+    kernel_names = {"input_transform": "input_transform_nhwc_tma", "tile_gemm_plain": {"fp32": "gemm_ffma_kernel", "fp32x3": "gemm_tc_split_kernel"}.get(args.dtype, "gemm_tc_kernel"),
                     "output_transform": "output_transform_direct", "tile_gemm_rowfused": "gemm_tc_z_kernel",
                     "direct_thin_input": "direct_small_c_kernel", "direct_tensor_core": "direct_tc2t_kernel + direct_tc2_kernel"}
     if t_hbm >= t_tc or args.dtype == "fp32":

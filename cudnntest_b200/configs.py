@@ -107,13 +107,43 @@ def run_variant(cfg_id, cfg, dtype, layout, wino, iters, peaks, flush):
                          "peaks": peaks["source"] + (" (FP32 FFMA: nominal)" if dtype == "fp32" else "")}}
 
 
+def measure_library_peaks(n=8192, reps=10):
+    """cuBLAS rates the peaks file does not hold, measured the way its BF16 figure was (torch.matmul, n^3, burst of
+    `reps` calls between two CUDA events): TF32 tensor-core GEMM and FP32 SGEMM on float operands."""
+    a = torch.randn((n, n), device="cuda")
+    b = torch.randn((n, n), device="cuda")
+    out = {}
+    old = torch.backends.cuda.matmul.allow_tf32
+    try:
+        for name, allow in (("tf32_tflops", True), ("fp32_sgemm_tflops", False)):
+            torch.backends.cuda.matmul.allow_tf32 = allow
+            for _ in range(3):
+                a @ b
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                a @ b
+            e1.record()
+            torch.cuda.synchronize()
+            out[name] = round(2.0 * n ** 3 * reps / (e0.elapsed_time(e1) * 1e-3) / 1e12, 1)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--config", type=int, nargs="*", default=[0, 1, 2, 3])
+    ap.add_argument("--library-peaks", action="store_true",
+                    help="print cuBLAS TF32 and FP32 SGEMM TFLOP/s of this GPU (one JSON line) and exit")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("no CUDA device: this library has no CPU path")
+    if args.library_peaks:
+        print(json.dumps(dict(measure_library_peaks(), what="torch.matmul 8192^3, float operands, burst of 10")))
+        return
     _lib.lib()
     peaks = load_peaks()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
