@@ -133,7 +133,16 @@ __global__ void __launch_bounds__(256, 2) input_transform_strip(const ITArgs a, 
         const int off = gw0 - ws;                                  // 0 .. VE-1
         const int nchunks = (off + COLS + VE - 1) / VE;
         const bool vec_ok = (a.W % VE) == 0 && ((a.sx.n | a.sx.c) % VE) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0;
-        for (int item = threadIdx.x; item < CH * A * nchunks; item += 256) {
+        // two phases, fully unrolled: every load of the thread is in flight before the first scatter into shared memory
+        // (a single loop makes each load wait for the one before it, one DRAM latency per pass)
+        constexpr int MAXCHUNKS = (COLS + 2 * (VE - 1) + VE - 1) / VE;
+        constexpr int PASSES = (CH * A * MAXCHUNKS + 255) / 256;
+        const int items = CH * A * nchunks;
+        uint4 held[PASSES];
+#pragma unroll
+        for (int i = 0; i < PASSES; ++i) {
+            const int item = threadIdx.x + 256 * i;
+            if (item >= items) continue;
             const int c_l = item % CH;
             const int rc = item / CH;
             const int r = rc % A, chunk = rc / A;
@@ -149,6 +158,17 @@ __global__ void __launch_bounds__(256, 2) input_transform_strip(const ITArgs a, 
                     vals[e] = (row_ok && w >= 0 && w < a.W) ? x[c * a.sx.c + gh * a.sx.h + w] : zero;
                 }
             }
+            held[i] = *reinterpret_cast<const uint4*>(vals);
+        }
+#pragma unroll
+        for (int i = 0; i < PASSES; ++i) {
+            const int item = threadIdx.x + 256 * i;
+            if (item >= items) continue;
+            const int c_l = item % CH;
+            const int rc = item / CH;
+            const int r = rc % A, chunk = rc / A;
+            __align__(16) TIn vals[VE];
+            *reinterpret_cast<uint4*>(vals) = held[i];
 #pragma unroll
             for (int e = 0; e < VE; ++e) {
                 const int col = chunk * VE + e - off;
@@ -199,7 +219,13 @@ __global__ void __launch_bounds__(256, 2) input_transform_batch(const ITArgs a, 
 
     // lanes run over the a*a patch positions of ONE channel (addresses inside one channel plane); the word column
     // is XOR-swizzled with the position so that this scatter and the transform's reads are both conflict free
-    for (int item = threadIdx.x; item < CH * A * A * NV; item += 256) {
+    // two phases, fully unrolled: all of the thread's loads are in flight before the first scatter
+    constexpr int PASSES = (CH * A * A * NV + 255) / 256;
+    uint4 held[PASSES];
+#pragma unroll
+    for (int i = 0; i < PASSES; ++i) {
+        const int item = threadIdx.x + 256 * i;
+        if (item >= CH * A * A * NV) continue;
         const int rs = item % (A * A);
         const int rc = item / (A * A);
         const int nv = rc % NV, c_l = rc / NV;
@@ -214,6 +240,18 @@ __global__ void __launch_bounds__(256, 2) input_transform_batch(const ITArgs a, 
 #pragma unroll
             for (int e = 0; e < VE; ++e) vals[e] = (ok && nb0 + n_l0 + e < a.ns) ? src[e] : zero;
         }
+        held[i] = *reinterpret_cast<const uint4*>(vals);
+    }
+#pragma unroll
+    for (int i = 0; i < PASSES; ++i) {
+        const int item = threadIdx.x + 256 * i;
+        if (item >= CH * A * A * NV) continue;
+        const int rs = item % (A * A);
+        const int rc = item / (A * A);
+        const int nv = rc % NV, c_l = rc / NV;
+        const int n_l0 = nv * VE;
+        __align__(16) TIn vals[VE];
+        *reinterpret_cast<uint4*>(vals) = held[i];
         const int word = (c_l / VEC) ^ (rs & 31);
 #pragma unroll
         for (int e = 0; e < VE; ++e) put_element<TIn>(patch, rs * IT_NB + n_l0 + e, word * VEC + (c_l % VEC), vals[e]);
