@@ -129,3 +129,17 @@ def test_random_shapes(cb):
         y = run_conv(x, wt, b, layout, dtype="fp32x3", wino=m, relu=True, pool=pool, pad=pad)
         assert y.shape == ref.shape
         assert np.abs(y - ref).max() <= TOL * max(np.abs(ref).max(), 1e-30), (layout, m, (n, c, h, w, k), pool, pad)
+
+
+@pytest.mark.parametrize("shape,layout,m", [((64, 256, 56, 56, 256), "NHWC", 4), ((64, 512, 28, 28, 512), "CHWN", 4),
+                                            ((64, 512, 28, 28, 512), "NHWC", 2)])
+def test_full_size_configs_properties(cb, shape, layout, m):
+    """BASELINE configs 1 and 2 at full size: the first two images against the oracle, the whole batch against itself
+    under a different slab size (bitwise), and image independence (permuting the batch permutes the output)."""
+    n, c, h, w, k = shape
+    x, wt, b = make_inputs(n, c, h, w, k, seed=0xC0DE0010 + m)
+    y = run_conv(x, wt, b, layout, dtype="fp32x3", wino=m, relu=True)
+    assert np.array_equal(y, run_conv(x, wt, b, layout, dtype="fp32x3", wino=m, relu=True, slab_images=5))
+    assert maxrel(y[:2], oracle.conv_f64(x[:2], wt, bias=b, relu=True)) <= TOL
+    perm = np.random.default_rng(0).permutation(n)
+    assert np.array_equal(run_conv(x[perm], wt, b, layout, dtype="fp32x3", wino=m, relu=True), y[perm])
