@@ -30,13 +30,13 @@ def summary(out):
 
 
 @pytest.mark.parametrize("opt", [0, 1, 2])
-@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("dtype", ["fp32", "fp32x3", "bf16"])
 def test_layout_compare_ours(opt, dtype):
     out = run("layoutCompare", "batch=4", "opt=%d" % opt, "layer=6", "dtype=" + dtype, "iters=5")
     assert len(re.findall(r"time:[0-9.]+ ms", out)) == 5
     assert "moduleConv error" not in out
     s = summary(out)
-    assert s["layout"] == ["NCHW", "NHWC", "CHWN"][opt] and s["max_err_sampled"] <= (1e-4 if dtype == "fp32" else 2e-2)
+    assert s["layout"] == ["NCHW", "NHWC", "CHWN"][opt] and s["max_err_sampled"] <= (1e-4 if dtype in ("fp32", "fp32x3") else 2e-2)
 
 
 def test_layout_compare_cudnn_best():
@@ -69,7 +69,7 @@ def test_net_test(mode):
     assert len(re.findall(r"time:[0-9.]+ ms", out)) == 3 and s["images_per_s"] > 0
 
 
-@pytest.mark.parametrize("dtype,layout,wino", [("bf16", "nhwc", 4), ("fp32", "nchw", 4), ("tf32", "chwn", 2)])
+@pytest.mark.parametrize("dtype,layout,wino", [("bf16", "nhwc", 4), ("fp32", "nchw", 4), ("tf32", "chwn", 2), ("fp32x3", "nhwc", 4)])
 def test_stage_bench(dtype, layout, wino):
     """Per-stage micro-benchmark on the nine VGG-16 shapes: every staged pipeline passes its host-side check and the
     weighted sums (the reference's weightedSum line and the JSON summary) are printed."""
@@ -80,7 +80,7 @@ def test_stage_bench(dtype, layout, wino):
     assert s["valid"] is True and s["weighted_us_vgg16"] > 0 and s["engine_weighted_us_vgg16"] > 0
 
 
-@pytest.mark.parametrize("mode,dtype", [(1, "bf16"), (0, "fp32"), (2, "bf16")])
+@pytest.mark.parametrize("mode,dtype", [(1, "bf16"), (0, "fp32"), (2, "bf16"), (1, "fp32x3")])
 def test_net_test_classifier_tail(mode, dtype):
     """netTest tail=1: fc14/fc15/fc16 + softmax + arg-max on the conv stack's output, checked by the harness against
     its host restatement (probabilities to 1e-4, same arg-max) for the first and the last image."""
