@@ -40,6 +40,8 @@ enum { WINO_NCHW = 0, WINO_NHWC = 1, WINO_CHWN = 2 };
  * every transform-domain operand is split into a TF32 head and a TF32 tail (x = hi + lo) and each FP32 product is
  * rebuilt from three TF32 products hi*hi + lo*hi + hi*lo (the dropped lo*lo term is below 2^-22 of the product):
  * FP32-level accuracy (inside the 1e-4 bound of the FP32 variant, not bit-identical to it) at tensor-core speed.
+ * Its transformed-filter buffer holds heads and tails, twice the FP32 variant's size (wino_filter_bytes reports it);
+ * the scratch has the FP32 variant's size (the input tiles are split inside the tile GEMM).
  * Accumulation is always FP32. */
 enum { WINO_FP32 = 0, WINO_TF32 = 1, WINO_BF16 = 2, WINO_FP32X3 = 3 };
 enum { WINO_OPERAND_AUTO = 0, WINO_OPERAND_BF16 = 1, WINO_OPERAND_F16 = 2 };
