@@ -16,6 +16,7 @@ _HEADER = os.path.join(os.path.dirname(_HERE), "include", "wino.h")
 NCHW, NHWC, CHWN = 0, 1, 2
 FP32, TF32, BF16, FP32X3 = 0, 1, 2, 3
 OPERAND_AUTO, OPERAND_BF16, OPERAND_F16 = 0, 1, 2
+OUT_SAME, OUT_FP32, OUT_BF16 = 0, 1, 2
 OK, E_BADARG, E_UNSUPPORTED, E_WORKSPACE, E_CUDA, E_TIMEOUT = 0, -1, -2, -3, -4, -5
 LAYOUT_CODES = {"NCHW": NCHW, "NHWC": NHWC, "CHWN": CHWN}
 DTYPE_CODES = {"fp32": FP32, "tf32": TF32, "bf16": BF16, "fp32x3": FP32X3}
@@ -31,7 +32,7 @@ class ConvDesc(ctypes.Structure):
     """struct wino_conv_desc"""
     _fields_ = [(n, ctypes.c_int) for n in (
         "layout_in", "layout_out", "n", "c", "h", "w", "k", "pad", "dtype", "operand", "wino",
-        "relu", "has_bias", "pool2x2", "slab_images", "reserved")]
+        "relu", "has_bias", "pool2x2", "slab_images", "out_dtype")]
 
 
 def declared_symbols():

@@ -26,8 +26,11 @@ def filter_shape(layout, k, c):
     return {0: (k, c, 3, 3), 1: (k, 3, 3, c), 2: (c, 3, 3, k)}[_code(LAYOUT_CODES, layout)]
 
 
+_OUT_CODES = {None: _lib.OUT_SAME, "same": _lib.OUT_SAME, "fp32": _lib.OUT_FP32, "bf16": _lib.OUT_BF16}
+
+
 def make_desc(n, c, h, w, k, layout="NHWC", layout_out=None, dtype="fp32", pad=1, wino=0, relu=False, bias=False,
-              pool=False, operand=0, slab_images=0):
+              pool=False, operand=0, slab_images=0, out_dtype=None):
     d = ConvDesc()
     d.layout_in = _code(LAYOUT_CODES, layout)
     d.layout_out = d.layout_in if layout_out is None else _code(LAYOUT_CODES, layout_out)
@@ -36,6 +39,7 @@ def make_desc(n, c, h, w, k, layout="NHWC", layout_out=None, dtype="fp32", pad=1
     d.operand, d.wino = operand, wino
     d.relu, d.has_bias, d.pool2x2 = int(relu), int(bias), int(pool)
     d.slab_images = slab_images
+    d.out_dtype = _OUT_CODES[out_dtype] if (out_dtype is None or isinstance(out_dtype, str)) else int(out_dtype)
     return d
 
 
@@ -56,12 +60,14 @@ def _require_cuda(*tensors):
 class WinoConv:
     """One 3x3 convolution: transformed filters are computed once, the scratch is owned here.
 
-    y = [pool2x2](relu(conv(x, w) + bias)) with x in `layout`, y in `layout_out`.
+    y = [pool2x2](relu(conv(x, w) + bias)) with x in `layout`, y in `layout_out`; out_dtype "fp32" / "bf16" stores y in
+    another element type than x (the mixed-precision hand-off between layers).
     """
 
     def __init__(self, n, c, h, w, k, layout="NHWC", layout_out=None, dtype="fp32", pad=1, wino=0, relu=False,
-                 bias=False, pool=False, operand=0, slab_images=0, device="cuda", workspace=None):
-        self.desc = make_desc(n, c, h, w, k, layout, layout_out, dtype, pad, wino, relu, bias, pool, operand, slab_images)
+                 bias=False, pool=False, operand=0, slab_images=0, device="cuda", workspace=None, out_dtype=None):
+        self.desc = make_desc(n, c, h, w, k, layout, layout_out, dtype, pad, wino, relu, bias, pool, operand, slab_images,
+                              out_dtype)
         L = lib()
         self.ws_bytes = L.wino_conv_workspace_bytes(ctypes.byref(self.desc))
         self.u_bytes = L.wino_filter_bytes(ctypes.byref(self.desc))
@@ -69,6 +75,8 @@ class WinoConv:
             raise _lib.WinoError(_lib.E_BADARG, L.wino_last_error_string().decode())
         self.device = torch.device(device)
         self.io_dtype = _TORCH_DTYPE[self.desc.dtype]
+        self.out_torch_dtype = {_lib.OUT_SAME: self.io_dtype, _lib.OUT_FP32: torch.float32,
+                                _lib.OUT_BF16: torch.bfloat16}[self.desc.out_dtype]
         self.u = torch.empty(self.u_bytes, dtype=torch.uint8, device=self.device)
         if workspace is not None and workspace.numel() * workspace.element_size() >= self.ws_bytes:
             self.workspace = workspace
@@ -97,7 +105,9 @@ class WinoConv:
         if x.dtype != self.io_dtype:
             raise ValueError("input dtype %s, expected %s" % (x.dtype, self.io_dtype))
         if out is None:
-            out = torch.empty(self.out_shape, dtype=self.io_dtype, device=x.device)
+            out = torch.empty(self.out_shape, dtype=self.out_torch_dtype, device=x.device)
+        elif out.dtype != self.out_torch_dtype:
+            raise ValueError("output dtype %s, expected %s" % (out.dtype, self.out_torch_dtype))
         ws = self.workspace
         check(lib().wino_conv_forward(ctypes.byref(self.desc), _ptr(x), _ptr(self.u), _ptr(self.bias), _ptr(out),
                                       _ptr(ws), ws.numel() * ws.element_size(), _stream()))

@@ -4,10 +4,11 @@
 // (comparison/wrapedConv_NCHW.cuh:335-492, wrapedConv_NHWC.cuh:24-112, wrapedConv_CHWN.cuh:16-82):
 // tiling arithmetic, then input transform -> tile GEMM -> output transform.  Differences by design:
 //   * the filter transform is a separate call made once per weight tensor;
-//   * the batch is processed in slabs of images sized so that one slab's V and M buffers stay resident
-//     in the 126 MB L2: the GEMM's product buffer is consumed by the output transform of the same slab
-//     before it is evicted, and the buffers are reused by the next slab, so the two largest
-//     intermediates of the pipeline do not round-trip through HBM;
+//   * the batch is processed in slabs of images that fit the caller's scratch (2 GiB by default, normally the
+//     whole batch: slabs small enough to stay in the 126 MB L2 were measured and lose, their kernels are
+//     launch- and latency-bound);
+//   * thin and medium-width tensor-core layers leave the Winograd pipeline for a direct implicit-GEMM kernel
+//     (direct_small_c.cu, direct_tc*.cu), chosen per shape and, for 512-channel layers, per batch size;
 //   * everything is asynchronous on the caller's stream; only wino_wraped_conv synchronises.
 #include <atomic>
 #include <cstdarg>
@@ -100,6 +101,9 @@ int make_geometry(const wino_conv_desc* d, Geometry* g) {
             break;
         default: return fail(WINO_E_BADARG, "bad dtype code %d", d->dtype);
     }
+    if (d->out_dtype != WINO_OUT_SAME && d->out_dtype != WINO_OUT_FP32 && d->out_dtype != WINO_OUT_BF16)
+        return fail(WINO_E_BADARG, "bad out_dtype code %d", d->out_dtype);
+    g->out_bf16 = d->out_dtype == WINO_OUT_SAME ? d->dtype == WINO_BF16 : d->out_dtype == WINO_OUT_BF16;
     g->oh = d->h + 2 * d->pad - 2;
     g->ow = d->w + 2 * d->pad - 2;
     if (d->pool2x2 && (g->oh < 2 || g->ow < 2)) return fail(WINO_E_BADARG, "pool2x2 needs an output of at least 2x2");
@@ -187,6 +191,14 @@ static bool force_rowfused(Geometry* g) {
     return true;
 }
 
+// ---- filter buffer layout ------------------------------------------------------------------------------------
+size_t wino_u_bytes(const wino_conv_desc& d, const Geometry& g) { return (size_t)g.a * g.a * d.k * g.crow * g.esize_op; }
+// where the packed filters of the direct kernel start in a buffer that holds both forms (direct_filter_mode == 2)
+size_t direct_filter_offset(const wino_conv_desc& d, const Geometry& g) { return (size_t)round_up_ll((long long)wino_u_bytes(d, g), 1024); }
+const void* direct_filters(const wino_conv_desc& d, const Geometry& g, const void* u) {
+    return direct_filter_mode(d) == 2 ? (const char*)u + direct_filter_offset(d, g) : u;
+}
+
 int check_device() {
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
@@ -247,12 +259,15 @@ int wino_device_status(void) {
 size_t wino_filter_bytes(const wino_conv_desc* d) {
     Geometry g;
     if (make_geometry(d, &g) != WINO_OK) return 0;
-    const size_t wino = (size_t)g.a * g.a * d->k * g.crow * g.esize_op;
-    // thin-input layers keep packed raw filters instead (always smaller); report the larger so either path fits
-    size_t need = wino;
-    if (direct_small_c_applies(*d) && direct_small_c_filter_bytes(*d) > need) need = direct_small_c_filter_bytes(*d);
-    if ((direct_tc_applies(*d) || direct_via_nhwc_applies(*d)) && direct_tc_filter_bytes(*d) > need) need = direct_tc_filter_bytes(*d);
-    return need;
+    if (direct_small_c_applies(*d)) {
+        // thin-input layers keep packed raw filters (always smaller); report the larger so either kernel's buffer fits
+        const size_t wino = wino_u_bytes(*d, g), thin = direct_small_c_filter_bytes(*d);
+        return thin > wino ? thin : wino;
+    }
+    const int mode = direct_filter_mode(*d);
+    if (mode == 1) { const size_t wino = wino_u_bytes(*d, g), dir = direct_tc_filter_bytes(*d); return dir > wino ? dir : wino; }
+    if (mode == 2) return direct_filter_offset(*d, g) + direct_tc_filter_bytes(*d);
+    return wino_u_bytes(*d, g);
 }
 
 size_t wino_conv_workspace_bytes(const wino_conv_desc* d) {
@@ -288,8 +303,13 @@ int wino_filter_transform(const wino_conv_desc* d, const void* w, void* u, wino_
     if (!w || !u) return fail(WINO_E_BADARG, "filter transform: NULL pointer");
     if ((rc = check_device())) return rc;
     if (direct_small_c_applies(*d)) return launch_direct_small_c_pack(*d, w, u, (cudaStream_t)stream);
-    if (direct_tc_applies(*d) || direct_via_nhwc_applies(*d)) return launch_direct_tc_pack(*d, w, u, (cudaStream_t)stream);
-    return launch_filter_transform(*d, g, w, u, (cudaStream_t)stream);
+    // The format of `u` depends on the shape, never on the batch size: where the engine picks between the direct kernel
+    // and the Winograd pipeline by batch size, `u` holds both forms and forward calls of any batch size can share it.
+    const int mode = direct_filter_mode(*d);
+    if (mode == 1) return launch_direct_tc_pack(*d, w, u, (cudaStream_t)stream);
+    if ((rc = launch_filter_transform(*d, g, w, u, (cudaStream_t)stream))) return rc;
+    if (mode == 2) return launch_direct_tc_pack(*d, w, (char*)u + direct_filter_offset(*d, g), (cudaStream_t)stream);
+    return WINO_OK;
 }
 
 int wino_stage_input_transform(const wino_conv_desc* d, const void* x, int n0, int ns, void* v, wino_stream_t stream) {
@@ -358,8 +378,9 @@ int wino_conv_forward(const wino_conv_desc* d, const void* x, const void* u, con
     if (d->has_bias && !bias) return fail(WINO_E_BADARG, "conv forward: has_bias set but bias is NULL");
     if ((rc = check_device())) return rc;
     if (direct_small_c_applies(*d)) return launch_direct_small_c(*d, g, x, u, bias, y, (cudaStream_t)stream);
-    if (direct_tc_applies(*d)) return launch_direct_tc(*d, g, x, u, bias, y, (cudaStream_t)stream);
-    if (direct_via_nhwc_applies(*d)) return launch_direct_via_nhwc(*d, g, x, u, bias, y, workspace, workspace_bytes, (cudaStream_t)stream);
+    if (direct_tc_applies(*d)) return launch_direct_tc(*d, g, x, direct_filters(*d, g, u), bias, y, (cudaStream_t)stream);
+    if (direct_via_nhwc_applies(*d))
+        return launch_direct_via_nhwc(*d, g, x, direct_filters(*d, g, u), bias, y, workspace, workspace_bytes, (cudaStream_t)stream);
     const int ns = slab_images(*d, g);
     const long long tp = tile_rows(g, ns);
     const size_t need = v_bytes(g, tp) + prod_bytes(g, tp) + 1024;

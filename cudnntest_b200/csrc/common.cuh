@@ -97,7 +97,8 @@ struct Geometry {
     int crow;         // U row length in elements: cp, or 2*cp for OP_TF32X3 (cp TF32 heads, then cp TF32 tails); V rows are always cp
     int kq;           // M row length
     int operand;      // OperandKind of V and U
-    int esize_io;     // bytes per activation element
+    int esize_io;     // bytes per activation element of x
+    int out_bf16;     // y is stored as bfloat16 (else float)
     int esize_op;     // bytes per V/U element
     int prod_kind;    // what the tile GEMM of wino_conv_forward writes: 0 = M (float), 1 = Z (float), 2 = Z (half)
     int prod_planes;  // a*a for M, a*m for Z
@@ -106,6 +107,11 @@ struct Geometry {
 
 inline int round_up(int x, int q) { return (x + q - 1) / q * q; }
 inline long long round_up_ll(long long x, long long q) { return (x + q - 1) / q * q; }
+
+// y stored in another element type than x: such layers always run the Winograd pipeline, whose output transform converts
+inline bool out_type_differs(const wino_conv_desc& d) {
+    return (d.out_dtype == WINO_OUT_FP32 && d.dtype == WINO_BF16) || (d.out_dtype == WINO_OUT_BF16 && d.dtype != WINO_BF16);
+}
 
 // ---- errors ------------------------------------------------------------------------------------------
 void set_error(const char* fmt, ...);
@@ -131,6 +137,9 @@ int run_conv_gemm(const Geometry& g, const void* v, const void* u, void* prod, i
 int run_gemm(const Geometry& g, const void* v, const void* u, float* m, int k, long long t_rows, long long tp,
              cudaStream_t st);
 int check_device();
+size_t wino_u_bytes(const wino_conv_desc& d, const Geometry& g);          // transformed filters U
+size_t direct_filter_offset(const wino_conv_desc& d, const Geometry& g);  // start of the packed filters when the buffer holds both
+const void* direct_filters(const wino_conv_desc& d, const Geometry& g, const void* u);   // what the direct kernels read
 
 // ---- measurement hooks -----------------------------------------------------------------------------------
 void count_launch();
@@ -154,6 +163,10 @@ int launch_gemm_ffma(const float* v, const float* u, float* m, int batches, long
                      int cp, int kq, cudaStream_t st);
 // direct convolution on tensor cores for thin, large-spatial NHWC BF16 layers, C = 64 / 128 (direct_tc.cu)
 bool direct_tc_applies(const wino_conv_desc& d);
+// What the filter buffer of this descriptor holds, whatever its batch size: 0 = transformed filters U only, 1 = filters
+// packed for the direct kernel only, 2 = U followed (on a 1 KiB boundary) by the packed filters, because the engine
+// picks between the two kernels by batch size (NHWC directly, the other layouts through NHWC staging).
+int direct_filter_mode(const wino_conv_desc& d);
 size_t direct_tc_filter_bytes(const wino_conv_desc& d);
 int launch_direct_tc_pack(const wino_conv_desc& d, const void* w, void* packed, cudaStream_t st);
 int launch_direct_tc(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,

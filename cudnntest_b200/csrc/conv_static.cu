@@ -19,6 +19,8 @@
 //     it needs to start at zero (each slab overwrites every element it later reads), but two calls that
 //     overlap on the GPU — different streams, or different host threads — race on it.  Serialise them.
 //   * no cudaMalloc, cudaFree or allocating library routine is called on this path.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace wino {
@@ -31,20 +33,21 @@ constexpr size_t kStaticScratchBytes = (size_t)WINO_STATIC_SCRATCH_BYTES;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-void* g_scratch_ptr[kMaxDevices] = {nullptr};
+std::atomic<void*> g_scratch_ptr[kMaxDevices];      // zero-initialised (static storage)
 
-// Device address of the scratch array on the current device; looked up once per device.
+// Device address of the scratch array on the current device; looked up once per device.  Two host threads that
+// make their first call on a device at the same moment both do the look-up and store the same address.
 int static_scratch(void** out) {
     int dev = -1;
     WINO_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= kMaxDevices) return fail(WINO_E_UNSUPPORTED, "static scratch: device index %d out of range", dev);
-    if (g_scratch_ptr[dev] == nullptr) {
-        void* p = nullptr;
+    void* p = g_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
         WINO_CUDA_CHECK(cudaGetSymbolAddress(&p, g_static_scratch));
         if (p == nullptr) return fail(WINO_E_CUDA, "static scratch: cudaGetSymbolAddress returned a null address");
-        g_scratch_ptr[dev] = p;
+        g_scratch_ptr[dev].store(p, std::memory_order_release);
     }
-    *out = g_scratch_ptr[dev];
+    *out = p;
     return WINO_OK;
 }
 
@@ -67,7 +70,7 @@ int wino_conv_forward_static(const wino_conv_desc* d, const void* x, const void*
     if (d->has_bias && !bias) return fail(WINO_E_BADARG, "conv forward (static scratch): has_bias set but bias is NULL");
     if ((rc = check_device())) return rc;
     if (direct_small_c_applies(*d)) return launch_direct_small_c(*d, g, x, u, bias, y, (cudaStream_t)stream);   // needs no scratch
-    if (direct_tc_applies(*d)) return launch_direct_tc(*d, g, x, u, bias, y, (cudaStream_t)stream);               // needs no scratch
+    if (direct_tc_applies(*d)) return launch_direct_tc(*d, g, x, direct_filters(*d, g, u), bias, y, (cudaStream_t)stream);   // needs no scratch
     if (direct_via_nhwc_applies(*d)) {      // NHWC staging of the whole batch has to fit the array
         const size_t need = direct_via_nhwc_staging_bytes(*d, g);
         if (need > kStaticScratchBytes)
@@ -76,7 +79,7 @@ int wino_conv_forward_static(const wino_conv_desc* d, const void* x, const void*
                         "use wino_conv_forward with caller-provided scratch for this size", need, kStaticScratchBytes);
         void* staging = nullptr;
         if ((rc = static_scratch(&staging))) return rc;
-        return launch_direct_via_nhwc(*d, g, x, u, bias, y, staging, kStaticScratchBytes, (cudaStream_t)stream);
+        return launch_direct_via_nhwc(*d, g, x, direct_filters(*d, g, u), bias, y, staging, kStaticScratchBytes, (cudaStream_t)stream);
     }
 
     // largest slab whose V + M (with the same 1 KiB carving as wino_conv_forward) fits the array
@@ -90,6 +93,9 @@ int wino_conv_forward_static(const wino_conv_desc* d, const void* x, const void*
     if (ns > 65535) ns = 65535;
     if (ns < 1) ns = 1;
     while (ns > 1 && v_bytes(g, tile_rows(g, ns)) + prod_bytes(g, tile_rows(g, ns)) + 1024 > kStaticScratchBytes) --ns;
+    // several slabs: start each on a multiple of 8 images where possible, as wino_conv_forward does, so that the CHWN
+    // kernels keep their 16-byte vectors along n (a slab that starts elsewhere is still correct, through scalar accesses)
+    if (ns < d->n && ns >= 8 && d->slab_images <= 0) ns -= ns % 8;
     if (v_bytes(g, tile_rows(g, ns)) + prod_bytes(g, tile_rows(g, ns)) + 1024 > kStaticScratchBytes)
         return fail(WINO_E_WORKSPACE, "conv forward (static scratch): a slab of %d image(s) exceeds the built-in %zu bytes", ns,
                     kStaticScratchBytes);

@@ -461,7 +461,7 @@ int run(DCArgs a, cudaStream_t st) {
 
 bool direct_small_c_applies(const wino_conv_desc& d) {
     static const bool off = [] { const char* e = getenv("WINO_NO_DIRECT"); return e && e[0] == '1'; }();
-    return !off && d.wino == 0 && d.c <= 3 && !d.pool2x2;
+    return !off && d.wino == 0 && d.c <= 3 && !d.pool2x2 && !out_type_differs(d);
 }
 
 size_t direct_small_c_filter_bytes(const wino_conv_desc& d) { return (size_t)d.k * 32 * (d.dtype == WINO_BF16 ? 2 : 4); }

@@ -294,25 +294,32 @@ int run(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const DtParams& p, cud
 
 }  // namespace
 
-bool direct_tc_applies(const wino_conv_desc& d) {
+// 0: this shape never takes the direct kernel, 1: it always does, 2: it does for small batches only.  Does not look
+// at d.n, so the format of the filter buffer (which follows this value) is the same for every batch size.
+int direct_tc_mode(const wino_conv_desc& d) {
     static const int mode = [] { const char* e = getenv("WINO_DIRECT_TC"); return e ? atoi(e) : 1; }();
-    if (mode == 0) return false;
+    if (mode == 0) return 0;
     // WINO_DIRECT_TC_MAXC forces the channel limit; by default the choice follows what was measured on B200 (batch 256):
     // up to 256 input channels the direct kernel beats the three-kernel Winograd pipeline (whose transform-domain
     // buffers are HBM-bound); at 512 channels Winograd's 4x fewer multiplies win, except on small images
     // (14 x 14) and small batches (fewer than 128 images of 28 x 28) where its tile GEMMs are too small to fill the
     // machine (512 -> 512 at 28 x 28, direct / Winograd: batch 64 0.162 / 0.179 ms, 128 0.319 / 0.317, 256 0.636 / 0.61).
     static const int max_c = [] { const char* e = getenv("WINO_DIRECT_TC_MAXC"); return (e && *e) ? atoi(e) : -1; }();
-    if (!(d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC && d.wino == 0)) return false;
+    if (!(d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC && d.wino == 0) || out_type_differs(d)) return 0;
     if (d.dtype == WINO_TF32) {
         // float storage, TF32 operands: CTA-pair kernel only (32 channels per 128-byte chunk).  At half the tensor rate
         // of BF16 the direct kernel stays ahead of the Winograd pipeline up to 256 channels.
-        if (!(d.c % 32 == 0 && direct_tc2_applies(d))) return false;
-        return max_c >= 0 ? d.c <= max_c : d.c <= 256;
+        if (!(d.c % 32 == 0 && direct_tc2_applies(d))) return 0;
+        return (max_c >= 0 ? d.c <= max_c : d.c <= 256) ? 1 : 0;
     }
-    if (!(d.dtype == WINO_BF16 && d.c % 64 == 0 && d.k % 8 == 0)) return false;
-    if (max_c >= 0) return d.c <= max_c;
-    return d.c <= 256 || (long long)d.h * d.w < 28 * 28 || (long long)d.n * d.h * d.w < 128LL * 28 * 28;
+    if (!(d.dtype == WINO_BF16 && d.c % 64 == 0 && d.k % 8 == 0)) return 0;
+    if (max_c >= 0) return d.c <= max_c ? 1 : 0;
+    return (d.c <= 256 || (long long)d.h * d.w < 28 * 28) ? 1 : 2;
+}
+
+bool direct_tc_applies(const wino_conv_desc& d) {
+    const int mode = direct_tc_mode(d);
+    return mode == 1 || (mode == 2 && (long long)d.n * d.h * d.w < 128LL * 28 * 28);
 }
 
 size_t direct_tc_filter_bytes(const wino_conv_desc& d) { return (size_t)9 * d.k * d.c * (d.dtype == WINO_BF16 ? 2 : 4); }
@@ -323,10 +330,16 @@ static wino_conv_desc nhwc_twin(const wino_conv_desc& d) {
     return t;
 }
 
-bool direct_via_nhwc_applies(const wino_conv_desc& d) {
+static bool via_nhwc_enabled(const wino_conv_desc& d) {
     static const bool off = [] { const char* e = getenv("WINO_DIRECT_RELAYOUT"); return e && e[0] == '0'; }();
-    if (off || (d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC)) return false;
-    return direct_tc_applies(nhwc_twin(d));
+    return !off && !(d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC);
+}
+
+bool direct_via_nhwc_applies(const wino_conv_desc& d) { return via_nhwc_enabled(d) && direct_tc_applies(nhwc_twin(d)); }
+
+int direct_filter_mode(const wino_conv_desc& d) {
+    if (d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC) return direct_tc_mode(d);
+    return via_nhwc_enabled(d) ? direct_tc_mode(nhwc_twin(d)) : 0;
 }
 
 static size_t round1k(size_t v) { return (v + 1023) & ~(size_t)1023; }

@@ -367,7 +367,7 @@ static int run(const wino_conv_desc& d, const Geometry& g, const OTArgs& a, cuda
 
 template <int A, bool ZF, typename TP>
 static int dispatch(const wino_conv_desc& d, const Geometry& g, const OTArgs& a, cudaStream_t st) {
-    const bool bf16 = d.dtype == WINO_BF16;
+    const bool bf16 = g.out_bf16 != 0;
     if (d.pool2x2)
         return bf16 ? run<A, true, ZF, TP, __nv_bfloat16>(d, g, a, st) : run<A, true, ZF, TP, float>(d, g, a, st);
     return bf16 ? run<A, false, ZF, TP, __nv_bfloat16>(d, g, a, st) : run<A, false, ZF, TP, float>(d, g, a, st);

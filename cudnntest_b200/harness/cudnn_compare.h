@@ -1,9 +1,7 @@
 // cuDNN comparator of the harnesses.
 //
-// wrapedConv_CuDNN keeps the reference's signature and mode numbering (comparison/wrapedConv_CuDNN.cuh:10-81:
-// mode 3/4 = NCHW WINOGRAD_NONFUSED / WINOGRAD, 5/6 = NHWC, FP32 with CUDNN_FMA_MATH), written against cuDNN 9.
-// Unlike the reference it keeps the workspace between calls, so a timed call does not include cudaMalloc/cudaFree
-// (comparison/wrapedConv_CuDNN.cuh:51-79 allocates inside the timed region).
+// wrapedConv_CuDNN with the reference's signature (comparison/wrapedConv_CuDNN.cuh:10-81) lives in
+// include/wino_cudnn_compat.cuh, next to the other drop-in headers; wino_cudnn_conv there returns the status.
 // cudnn_best_forward times every algorithm cudnnFindConvolutionForwardAlgorithm reports as working for a given
 // tensor format, data type and math mode and returns the fastest: the "cuDNN best" baseline.
 #pragma once
@@ -13,6 +11,7 @@
 #include <string>
 
 #include "harness_common.h"
+#include "wino_cudnn_compat.cuh"
 
 #define HCHECK_CUDNN(expr)                                                                               \
     do {                                                                                                 \
@@ -46,41 +45,6 @@ struct CudnnWorkspace {
 inline CudnnWorkspace& cudnn_workspace() {
     static CudnnWorkspace w;
     return w;
-}
-
-// Returns the cuDNN status as an int (0 = success); prints a line and leaves *output untouched on failure.
-inline int wrapedConv_CuDNN(int bat4Conv, int inside, int& chn, int numOfFilter, int padding, float* m1, float* m2,
-                            float** output, int mode, cudnnHandle_t& handle, cudnnTensorDescriptor_t& xdesc,
-                            cudnnTensorDescriptor_t& ydesc, cudnnFilterDescriptor_t& wdesc,
-                            cudnnConvolutionDescriptor_t& conv_desc) {
-    if (mode < 3 || mode > 6) {
-        printf("The mode is not right\n");
-        return -1;
-    }
-    const cudnnTensorFormat_t fmt = (mode == 3 || mode == 4) ? CUDNN_TENSOR_NCHW : CUDNN_TENSOR_NHWC;
-    const cudnnConvolutionFwdAlgo_t algo =
-        (mode == 3 || mode == 5) ? CUDNN_CONVOLUTION_FWD_ALGO_WINOGRAD_NONFUSED : CUDNN_CONVOLUTION_FWD_ALGO_WINOGRAD;
-    const int oside = inside + 2 * padding - 2;
-    HCHECK_CUDNN(cudnnSetTensor4dDescriptor(xdesc, fmt, CUDNN_DATA_FLOAT, bat4Conv, chn, inside, inside));
-    HCHECK_CUDNN(cudnnSetTensor4dDescriptor(ydesc, fmt, CUDNN_DATA_FLOAT, bat4Conv, numOfFilter, oside, oside));
-    HCHECK_CUDNN(cudnnSetFilter4dDescriptor(wdesc, CUDNN_DATA_FLOAT, fmt, numOfFilter, chn, 3, 3));
-    HCHECK_CUDNN(cudnnSetConvolution2dDescriptor(conv_desc, padding, padding, 1, 1, 1, 1, CUDNN_CROSS_CORRELATION, CUDNN_DATA_FLOAT));
-    HCHECK_CUDNN(cudnnSetConvolutionMathType(conv_desc, CUDNN_FMA_MATH));
-    size_t ws = 0;
-    cudnnStatus_t st = cudnnGetConvolutionForwardWorkspaceSize(handle, xdesc, wdesc, conv_desc, ydesc, algo, &ws);
-    if (st != CUDNN_STATUS_SUCCESS) {
-        printf("cuDNN %s not available for this shape: %s\n", fwd_algo_name(algo), cudnnGetErrorString(st));
-        return (int)st;
-    }
-    void* extra = cudnn_workspace().reserve(ws ? ws : 16);
-    const float one = 1.f, zero = 0.f;
-    st = cudnnConvolutionForward(handle, &one, xdesc, m1, wdesc, m2, conv_desc, algo, extra, ws, &zero, ydesc, *output);
-    if (st != CUDNN_STATUS_SUCCESS) {
-        printf("cuDNN %s failed: %s\n", fwd_algo_name(algo), cudnnGetErrorString(st));
-        return (int)st;
-    }
-    chn = numOfFilter;
-    return 0;
 }
 
 struct CudnnBest {

@@ -154,7 +154,7 @@ int main(int argc, char** argv) {
             for (int i = 0; i < iters + 2; ++i) {
                 int chn = c;
                 HCHECK_CUDA(cudaEventRecord(e0));
-                const int rc = wrapedConv_CuDNN(n, h, chn, k, pad, (float*)xd, (float*)wd, &out, opt, handle, xdesc, ydesc, wdesc, cdesc);
+                const int rc = wino_cudnn_conv(n, h, chn, k, pad, (float*)xd, (float*)wd, &out, opt, handle, xdesc, ydesc, wdesc, cdesc);
                 HCHECK_CUDA(cudaDeviceSynchronize());
                 HCHECK_CUDA(cudaEventRecord(e1));
                 HCHECK_CUDA(cudaEventSynchronize(e1));

@@ -5,7 +5,10 @@
 // ReLU, a 2x2 max-pool after each of the five blocks.  Command line as there: `netTest set batch=B mode=M`
 //   mode 0/1/2   this library in NCHW / NHWC / CHWN: one wino_conv_forward per layer (bias, ReLU and the pool
 //                fused into the output transform) instead of the reference's 6-7 kernels per layer
-//                (layoutManager + addBias + relu (+ pool), Network.h:456-519, :603-669)
+//                (layoutManager + addBias + relu (+ pool), Network.h:456-519, :603-669).  In mode 2 the last
+//                convolution reads CHWN and writes NCHW, the hand-off to the classifier that the reference makes
+//                at conv13 (vggCUDNN.cu:173-176); with tail=1 it also writes FP32 whatever the storage type of the
+//                stack, so the classifier's FP32 GEMM reads it without a relayout or conversion pass
 //   mode 3/4     cuDNN in NCHW / NHWC: fastest forward algorithm per layer + cudnnAddTensor +
 //                cudnnActivationForward (+ cudnnPoolingForward), i.e. Network.h:171-312, :314-444
 // plus dtype=fp32|fp32x3|tf32|bf16 (default bf16), rounds= (default 10), tail=0|1.  With tail=1 the classifier tail of the
@@ -81,7 +84,8 @@ int main(int argc, char** argv) {
     HCHECK_CUDA(cudaEventCreate(&e1));
     std::vector<float> times;
     std::string what;
-    const void* final_out = nullptr;      // pooled output of conv13: (n, 512, 7, 7) in `layout`
+    const void* final_out = nullptr;      // pooled output of conv13: (n, 512, 7, 7) in `final_layout`, stored as `final_dtype`
+    int final_layout = layout, final_dtype = dtype;
 
     if (mode <= 2) {
         std::vector<wino_conv_desc> desc(13);
@@ -93,6 +97,10 @@ int main(int argc, char** argv) {
             d.layout_in = d.layout_out = layout;
             d.n = n; d.c = kVgg[l].c; d.h = d.w = kVgg[l].s; d.k = kVgg[l].k; d.pad = 1;
             d.dtype = dtype; d.relu = 1; d.has_bias = 1; d.pool2x2 = kVgg[l].pool;
+            if (mode == 2 && l == 12) {        // conv13.layout_in = CHWN, layout_out = NCHW (vggCUDNN.cu:173-176)
+                d.layout_out = final_layout = WINO_NCHW;
+                if (tail) { d.out_dtype = WINO_OUT_FP32; final_dtype = dtype == WINO_BF16 ? WINO_FP32 : dtype; }
+            }
             const size_t ub = wino_filter_bytes(&d), wb = wino_conv_workspace_bytes(&d);
             if (!ub || !wb) { fprintf(stderr, "libwino: %s\n", wino_last_error_string()); return 3; }
             HCHECK_CUDA(cudaMalloc(&u[l], ub));
@@ -214,10 +222,10 @@ int main(int argc, char** argv) {
     if (tail && final_out) {
         ClassifierTail ct;
         ct.init(n);
-        ct.forward(final_out, layout, dtype);          // warm-up (cuBLAS set-up)
+        ct.forward(final_out, final_layout, final_dtype);          // warm-up (cuBLAS set-up)
         HCHECK_CUDA(cudaDeviceSynchronize());
         HCHECK_CUDA(cudaEventRecord(e0));
-        ct.forward(final_out, layout, dtype);
+        ct.forward(final_out, final_layout, final_dtype);
         HCHECK_CUDA(cudaEventRecord(e1));
         HCHECK_CUDA(cudaEventSynchronize(e1));
         float tail_ms;

@@ -45,6 +45,7 @@ enum { WINO_NCHW = 0, WINO_NHWC = 1, WINO_CHWN = 2 };
  * Accumulation is always FP32. */
 enum { WINO_FP32 = 0, WINO_TF32 = 1, WINO_BF16 = 2, WINO_FP32X3 = 3 };
 enum { WINO_OPERAND_AUTO = 0, WINO_OPERAND_BF16 = 1, WINO_OPERAND_F16 = 2 };
+enum { WINO_OUT_SAME = 0, WINO_OUT_FP32 = 1, WINO_OUT_BF16 = 2 };
 
 enum {
     WINO_OK = 0,
@@ -61,12 +62,18 @@ typedef struct wino_conv_desc {
     int dtype;                 /* WINO_FP32 / WINO_TF32 / WINO_BF16 / WINO_FP32X3                    */
     int operand;               /* WINO_BF16 only: format of the transformed operands; AUTO = F16 (FP16
                                   operands keep both tile sizes inside the 5e-3 tolerance)          */
-    int wino;                  /* output tile size m of F(m x m, 3x3): 2 or 4.  0 = the engine chooses:
-                                  F(4x4,3x3), except that thin NHWC layers of the tensor-core variants run
-                                  a direct tensor-core kernel (C <= 3; BF16 with C = 64 or 128)          */
+    int wino;                  /* output tile size m of F(m x m, 3x3): 2 or 4.  0 = the engine chooses per shape:
+                                  F(4x4,3x3), or a direct implicit-GEMM tensor-core kernel where that is faster
+                                  (C <= 3; BF16 with C a multiple of 64, TF32 with C a multiple of 32, up to 256
+                                  channels, and wider BF16 layers on small images or small batches; NCHW / CHWN
+                                  reach it through NHWC staging in the caller's scratch)                  */
     int relu, has_bias, pool2x2; /* epilogue fused into the output transform: y = pool(relu(conv+b)) */
     int slab_images;           /* images transformed per pass; 0 = as many as fit a 2 GiB scratch       */
-    int reserved;
+    int out_dtype;             /* element type of y: WINO_OUT_SAME (that of x), WINO_OUT_FP32 or WINO_OUT_BF16: the
+                                  mixed-precision hand-off between layers, e.g. the last BF16 convolution of a
+                                  network writing FP32 NCHW for the FP32 classifier that follows
+                                  (netTest/cudnn_test_0124/VGG_Batched/vggCUDNN.cu:173-176 changes layout there).
+                                  A y type that differs from x always takes the Winograd pipeline.        */
 } wino_conv_desc;
 
 const char* wino_last_error_string(void);
@@ -95,8 +102,10 @@ int wino_filter_transform(const wino_conv_desc* d, const void* w, void* u, wino_
  * (comparison/wrapedConv_NCHW.cuh:335-492, wrapedConv_NHWC.cuh:24-112, wrapedConv_CHWN.cuh:16-82),
  * the six convLayoutTrans_X_to_Y (comparison/DataLayoutTrans.cuh:9-584) when layout_out differs, and
  * the separate bias / ReLU / pool passes of netTest/cudnn_test_0124/VGG_Batched/Network.h:456-519.
- * `u` comes from wino_filter_transform with the same descriptor (it holds the transformed filters, or the
- * repacked raw filters where the descriptor selects a direct kernel).  bias: K floats (16-byte aligned) or NULL. */
+ * `u` comes from wino_filter_transform with a descriptor that may differ in n and slab_images only: its format
+ * follows the other fields, never the batch size (transformed filters, filters repacked for a direct kernel, or both
+ * where the engine picks the kernel by batch size).
+ * bias: K floats (16-byte aligned) or NULL. */
 int wino_conv_forward(const wino_conv_desc* d, const void* x, const void* u, const float* bias, void* y,
                       void* workspace, size_t workspace_bytes, wino_stream_t stream);
 
@@ -145,7 +154,7 @@ int wino_maxpool2x2(int layout, int n, int c, int h, int w, int dtype, const voi
  * per-stage breakdown of comparison/wrapedConv_NCHW.cuh:88-138).  wino_profile_read synchronises the
  * device, adds up the elapsed milliseconds and launches per kernel class since the last read (index 0 input
  * transform, 1 plain tile GEMM (tensor-core or FFMA), 2 output transform, 3 filter transform, 4 row-fused
- * tile GEMM, 5 thin-input (C <= 3) direct convolution, 6 direct tensor-core convolution (C = 64 / 128), 7 unused)
+ * tile GEMM, 5 thin-input (C <= 3) direct convolution, 6 direct tensor-core convolution, 7 unused)
  * and clears the record. */
 long long wino_launch_count(void);
 int wino_profile_enable(int on);

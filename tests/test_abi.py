@@ -75,6 +75,21 @@ def test_buffer_sizes(L, shape, dtype, m):
     assert ws_all <= n * (v_img + a * a * tiles * kq * 4) + a * a * 128 * (cp * es + kq * 4) + 4096
 
 
+@pytest.mark.parametrize("layout", ["NCHW", "NHWC", "CHWN"])
+@pytest.mark.parametrize("dtype", ["fp32", "tf32", "bf16", "fp32x3"])
+@pytest.mark.parametrize("chw", [(3, 224, 224, 64), (64, 56, 56, 64), (256, 56, 56, 256), (512, 28, 28, 512), (512, 14, 14, 512)])
+def test_filter_buffer_does_not_depend_on_the_batch(L, layout, dtype, chw):
+    """Weights are transformed once and used with any batch size: the size (and with it the format) of the filter
+    buffer must not change with n, although the engine's kernel choice does (512 channels at 28 x 28: direct kernel
+    below 128 images, Winograd from there on, so that buffer holds both forms)."""
+    c, h, w, k = chw
+    sizes = {L.wino_filter_bytes(ctypes.byref(cb.make_desc(n, c, h, w, k, layout=layout, dtype=dtype))) for n in (1, 8, 127, 128, 256)}
+    assert len(sizes) == 1 and 0 not in sizes
+    if dtype == "bf16" and c == 512 and h == 28:
+        u_wino = 36 * k * c * 2
+        assert sizes == {u_wino + 9 * k * c * 2}
+
+
 def test_legacy_workspaces_cover_the_slabs(L):
     """The reference callers' minimum buffer sizes hold this library's V, U, M for any slab."""
     for (n, h, c, k) in ((1, 224, 3, 64), (8, 56, 64, 64), (64, 28, 512, 512), (3, 14, 20, 130)):

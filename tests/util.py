@@ -34,7 +34,7 @@ def to_dev(a, torch_dtype=None):
 
 
 def run_conv(x, wt, b, layout, layout_out=None, dtype="fp32", wino=0, relu=False, pool=False, pad=1, operand=0,
-             slab_images=0):
+             slab_images=0, out_dtype=None):
     """x, wt NCHW/KCRS numpy -> result as a float32 NCHW numpy array, through WinoConv (C ABI)."""
     import torch
     import cudnntest_b200 as cb
@@ -43,7 +43,7 @@ def run_conv(x, wt, b, layout, layout_out=None, dtype="fp32", wino=0, relu=False
     k = wt.shape[0]
     tdt = torch.bfloat16 if dtype == "bf16" else torch.float32
     conv = cb.WinoConv(n, c, h, w, k, layout=layout, layout_out=lo, dtype=dtype, pad=pad, wino=wino, relu=relu,
-                       bias=b is not None, pool=pool, operand=operand, slab_images=slab_images)
+                       bias=b is not None, pool=pool, operand=operand, slab_images=slab_images, out_dtype=out_dtype)
     conv.set_filter(to_dev(oracle.filter_to_layout(wt, layout), tdt), None if b is None else to_dev(b))
     y = conv(to_dev(oracle.to_layout(x, layout), tdt))
     cb.device_status()
