@@ -86,6 +86,8 @@ def lib():
     L.wino_wraped_conv.argtypes = [I, I, I, I, ctypes.POINTER(I), I, I, V, V, V, V, V, ctypes.POINTER(V)]
     L.wino_layout_convert.argtypes = [I, I, I, I, I, I, I, V, V, V]
     L.wino_maxpool2x2.argtypes = [I, I, I, I, I, I, V, V, V]
+    L.wino_selftest_wait_timeout.argtypes = [I, V]
+    L.wino_selftest_wait_timeout.restype = I
     L.wino_stage_tile_rows.restype = ctypes.c_longlong
     L.wino_stage_tile_rows.argtypes = [P, I]
     L.wino_stage_cp.argtypes = [P]

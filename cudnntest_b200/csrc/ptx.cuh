@@ -45,7 +45,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // was raised by another thread) or if this wait ran out of time, in which case it raises the flag and
 // records `code` in the global status word (first failure wins).
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                                  int code) {
+                                                  int code, unsigned long long limit_ns = WAIT_LIMIT_NS) {
     unsigned long long t0 = 0;
     for (uint32_t it = 0;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -53,7 +53,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
             if (*abort_flag) return false;
             const unsigned long long now = global_timer();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_LIMIT_NS) {
+            else if (now - t0 > limit_ns) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 return false;
@@ -63,8 +63,9 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 }
 
 // The same wait executed by all 32 lanes of a warp, with one verdict for the warp (so that warp-uniform code can follow).
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-    const bool ok = mbar_wait_bounded(bar, parity, abort_flag, status, code);
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                               unsigned long long limit_ns = WAIT_LIMIT_NS) {
+    const bool ok = mbar_wait_bounded(bar, parity, abort_flag, status, code, limit_ns);
     return __all_sync(0xffffffffu, ok);
 }
 // One lane of a fully active warp (the same lane every time it is called by that warp).

@@ -1,10 +1,40 @@
 // Host-side helpers of the TMA / mbarrier kernels: tensor-map encoding through the driver entry point (no
 // link-time dependency on libcuda), SM count, and the device status word of the bounded waits.
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
 #include "ptx.cuh"
 
 namespace wino {
 
 namespace {
+
+// Cache of encoded tensor maps.  A tensor map is a pure function of (element type, rank, base address, extents,
+// strides, box, swizzle), so a forward call that comes back with the same buffers and shapes (every call of a
+// layoutCompare-style benchmark loop, every layer of a network whose activations ping-pong between two buffers)
+// finds its maps here instead of paying cuTensorMapEncodeTiled two or three times per kernel launch.
+struct MapKey {
+    unsigned long long base, dims[5], strides[4];
+    unsigned box[5];
+    int dt, rank, swizzle, pad;
+    bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        const unsigned long long* w = reinterpret_cast<const unsigned long long*>(&k);
+        unsigned long long h = 1469598103934665603ull;
+        for (size_t i = 0; i < sizeof(MapKey) / 8; ++i) { h ^= w[i]; h *= 1099511628211ull; }
+        return (size_t)h;
+    }
+};
+static_assert(sizeof(MapKey) % 8 == 0, "MapKey is hashed as 64-bit words");
+constexpr size_t kMapCacheLimit = 4096;       // entries (160 bytes each); the cache is emptied when it is full
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash>& map_cache() {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> c;
+    return c;
+}
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -33,6 +63,17 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const 
                       const unsigned long long* strides_bytes, const unsigned* box, bool swizzle_128) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(WINO_E_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    if (rank < 1 || rank > 5) return fail(WINO_E_BADARG, "tensor map rank %d", rank);
+    MapKey key;
+    memset(&key, 0, sizeof(key));
+    key.base = (unsigned long long)(uintptr_t)base; key.dt = (int)dt; key.rank = rank; key.swizzle = swizzle_128 ? 1 : 0;
+    for (int i = 0; i < rank; ++i) { key.dims[i] = dims[i]; key.box[i] = box[i]; }
+    for (int i = 0; i + 1 < rank; ++i) key.strides[i] = strides_bytes[i];
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        auto it = map_cache().find(key);
+        if (it != map_cache().end()) { *map = it->second; return WINO_OK; }
+    }
     cuuint64_t d[5], s[4];
     cuuint32_t b[5], e[5];
     for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; e[i] = 1; }
@@ -41,6 +82,11 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const 
                     swizzle_128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(WINO_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        if (map_cache().size() >= kMapCacheLimit) map_cache().clear();
+        map_cache().emplace(key, *map);
+    }
     return WINO_OK;
 }
 

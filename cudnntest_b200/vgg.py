@@ -129,15 +129,18 @@ class VGG16ConvStack:
 
     __call__ = forward
 
-    def capture(self, x):
+    def capture(self, x, prologue=None):
         """Record one forward pass over the fixed input buffer x into a CUDA graph (the 13-layer chain is short enough
         for launch gaps to show).  Runs one eager pass first: per-device set-up done on a kernel's first call cannot be
-        captured.  Returns (graph, output view); graph.replay() recomputes the output from the current contents of x."""
+        captured.  `prologue`, if given, is called at the head of the captured region (the benchmark's L2 flush).
+        Returns (graph, output view); graph.replay() recomputes the output from the current contents of x."""
         self.forward(x)
         torch.cuda.synchronize()
         before = _lib.lib().wino_launch_count()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
+            if prologue is not None:
+                prologue()
             y = self.forward(x)
         self.launches_per_forward = _lib.lib().wino_launch_count() - before
         return graph, y

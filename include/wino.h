@@ -147,6 +147,13 @@ int wino_layout_convert(int layout_src, int layout_dst, int n, int c, int h, int
 int wino_maxpool2x2(int layout, int n, int c, int h, int w, int dtype, const void* in, void* out,
                     wino_stream_t stream);
 
+/* TEST-ONLY: launches one small CTA in which a bounded device-side wait runs out after `limit_ms` (1 ... 1000)
+ * milliseconds, because nothing ever arrives on its mbarrier.  The CTA records the give-up, lets its other warps leave
+ * through the abort flag, frees its tensor memory and returns by itself; the next wino_device_status() returns
+ * WINO_E_TIMEOUT once, the one after that WINO_OK.  No counterpart in the reference (its kernels have no waits to
+ * bound); it exists so that the give-up path of the tensor-core kernels' waits can be exercised without a fault. */
+int wino_selftest_wait_timeout(int limit_ms, wino_stream_t stream);
+
 /* ---- measurement hooks ----------------------------------------------------------------------------
  * wino_launch_count: kernels launched by this process through the library so far.
  * wino_profile_enable(1): from now on every kernel launched by wino_conv_forward / wino_filter_transform is
