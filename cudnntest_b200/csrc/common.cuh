@@ -169,11 +169,13 @@ bool direct_tc_applies(const wino_conv_desc& d);
 int direct_filter_mode(const wino_conv_desc& d);
 size_t direct_tc_filter_bytes(const wino_conv_desc& d);
 int launch_direct_tc_pack(const wino_conv_desc& d, const void* w, void* packed, cudaStream_t st);
+// y_nchw: store the result NCHW although d says NHWC (only where direct_tc_stores_nchw(d), direct_tc.cuh)
 int launch_direct_tc(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,
-                     cudaStream_t st);
-// BF16 layers in NCHW / CHWN whose NHWC twin takes the direct kernel: the activations are relaid out to NHWC staging
-// buffers around the direct kernel (two extra passes over x and y cost less HBM time than the Winograd pipeline's
-// transform-domain buffers).  staging bytes = what `scratch` must hold; the filters are packed as for the direct kernel.
+                     cudaStream_t st, bool y_nchw = false);
+// BF16 / TF32 layers in NCHW / CHWN whose NHWC twin takes the direct kernel: the activations are relaid out to NHWC
+// staging buffers around the direct kernel (extra passes over x and y cost less HBM time than the Winograd pipeline's
+// transform-domain buffers); an NCHW result is stored by the filters-as-M kernel itself, without a pass over y.
+// staging bytes = what `scratch` must hold; the filters are packed as for the direct kernel.
 bool direct_via_nhwc_applies(const wino_conv_desc& d);
 size_t direct_via_nhwc_staging_bytes(const wino_conv_desc& d, const Geometry& g);
 int launch_direct_via_nhwc(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,

@@ -344,11 +344,14 @@ int direct_filter_mode(const wino_conv_desc& d) {
 
 static size_t round1k(size_t v) { return (v + 1023) & ~(size_t)1023; }
 
+// the kernel behind the NHWC twin stores an NCHW result itself: no staging of y, no relayout pass after it
+static bool y_stored_in_place(const wino_conv_desc& d) { return d.layout_out == WINO_NCHW && direct_tc_stores_nchw(nhwc_twin(d)); }
+
 size_t direct_via_nhwc_staging_bytes(const wino_conv_desc& d, const Geometry& g) {
     const size_t es = d.dtype == WINO_BF16 ? 2 : 4;
     size_t need = 1024;
     if (d.layout_in != WINO_NHWC) need += round1k((size_t)d.n * d.c * d.h * d.w * es);
-    if (d.layout_out != WINO_NHWC) need += round1k((size_t)d.n * d.k * g.ph * g.pw * es);
+    if (d.layout_out != WINO_NHWC && !y_stored_in_place(d)) need += round1k((size_t)d.n * d.k * g.ph * g.pw * es);
     return need;
 }
 
@@ -368,10 +371,11 @@ int launch_direct_via_nhwc(const wino_conv_desc& d, const Geometry& g, const voi
         if ((rc = launch_relayout(d.layout_in, WINO_NHWC, d.n, d.c, d.h, d.w, es, x, xs, st))) return rc;
         xin = xs;
     }
-    if (d.layout_out != WINO_NHWC) yout = (void*)p;
+    const bool in_place = y_stored_in_place(d);
+    if (d.layout_out != WINO_NHWC && !in_place) yout = (void*)p;
     const wino_conv_desc t = nhwc_twin(d);
-    if ((rc = launch_direct_tc(t, g, xin, packed, bias, yout, st))) return rc;
-    if (d.layout_out != WINO_NHWC) return launch_relayout(WINO_NHWC, d.layout_out, d.n, d.k, g.ph, g.pw, es, yout, y, st);
+    if ((rc = launch_direct_tc(t, g, xin, packed, bias, yout, st, in_place))) return rc;
+    if (d.layout_out != WINO_NHWC && !in_place) return launch_relayout(WINO_NHWC, d.layout_out, d.n, d.k, g.ph, g.pw, es, yout, y, st);
     return WINO_OK;
 }
 
@@ -390,9 +394,10 @@ int launch_direct_tc_pack(const wino_conv_desc& d, const void* w, void* packed, 
 }
 
 int launch_direct_tc(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,
-                     cudaStream_t st) {
+                     cudaStream_t st, bool y_nchw) {
     if (d.n == 0) return WINO_OK;
-    if (direct_tc2_applies(d)) return launch_direct_tc2(d, g, x, packed, bias, y, st);
+    if (direct_tc2_applies(d)) return launch_direct_tc2(d, g, x, packed, bias, y, st, y_nchw);
+    if (y_nchw) return fail(WINO_E_UNSUPPORTED, "direct conv: the single-CTA kernel stores NHWC only");
     if (((uintptr_t)x | (uintptr_t)packed | (uintptr_t)y | (d.has_bias ? (uintptr_t)bias : 0)) & 15)
         return fail(WINO_E_BADARG, "direct conv: buffers (and the bias) must be 16-byte aligned");
     DtParams p;
@@ -400,7 +405,7 @@ int launch_direct_tc(const wino_conv_desc& d, const Geometry& g, const void* x, 
     p.N = d.n; p.OH = g.oh; p.OW = g.ow; p.K = d.k; p.pad = d.pad; p.PH = g.ph; p.PW = g.pw;
     p.tiles_x = (g.ow + DT_TW - 1) / DT_TW; p.tiles_y = (g.oh + DT_TH - 1) / DT_TH;
     p.cchunks = d.c / 64;
-    p.relu = d.relu; p.pool = d.pool2x2;
+    p.relu = d.relu; p.pool = d.pool2x2; p.y_nchw = 0;
     int rc = status_word(&p.status);
     if (rc) return rc;
     const int bn = d.k >= 128 ? 128 : 64;

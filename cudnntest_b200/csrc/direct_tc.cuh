@@ -22,6 +22,7 @@ struct DtParams {
     int PH, PW;                  // stored output size (after the optional pool)
     int tiles_x, tiles_y, nblocks, cchunks;
     int relu, pool;
+    int y_nchw;                  // filters-as-M kernel only: y is stored NCHW (pixels contiguous) instead of NHWC
     uint32_t idesc;
     int* status;
 };
@@ -29,11 +30,13 @@ struct DtParams {
 // CTA-pair kernel (direct_tc2.cu); same packed filters and tensor maps as the single-CTA kernel
 bool direct_tc2_applies(const wino_conv_desc& d);
 int launch_direct_tc2(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,
-                      cudaStream_t st);
+                      cudaStream_t st, bool y_nchw = false);
 
 // CTA-pair kernel with the filters as the M operand, K >= 256 (direct_tc2t.cu)
 bool direct_tc2t_applies(const wino_conv_desc& d);
 int launch_direct_tc2t(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,
-                       cudaStream_t st);
+                       cudaStream_t st, bool y_nchw = false);
+// d: an NHWC descriptor.  True if the kernel chosen for it can store its result NCHW itself (launch_direct_tc with y_nchw).
+bool direct_tc_stores_nchw(const wino_conv_desc& d);
 
 }  // namespace wino

@@ -402,13 +402,16 @@ bool direct_tc2_applies(const wino_conv_desc& d) {
     return d.dtype == WINO_BF16 ? d.c % 64 == 0 : d.dtype == WINO_TF32 ? d.c % 32 == 0 : false;
 }
 
+bool direct_tc_stores_nchw(const wino_conv_desc& d) {
+    int obn, omt, ores;
+    return direct_tc2_applies(d) && direct_tc2t_applies(d) && !variant_override(obn, omt, ores);
+}
+
 int launch_direct_tc2(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,
-                      cudaStream_t st) {
+                      cudaStream_t st, bool y_nchw) {
     if (d.n == 0) return WINO_OK;
-    {
-        int obn, omt, ores;
-        if (direct_tc2t_applies(d) && !variant_override(obn, omt, ores)) return launch_direct_tc2t(d, g, x, packed, bias, y, st);
-    }
+    if (direct_tc_stores_nchw(d)) return launch_direct_tc2t(d, g, x, packed, bias, y, st, y_nchw);
+    if (y_nchw) return fail(WINO_E_UNSUPPORTED, "direct conv (CTA pairs): this kernel variant stores NHWC only");
     if (((uintptr_t)x | (uintptr_t)packed | (uintptr_t)y | (d.has_bias ? (uintptr_t)bias : 0)) & 15)
         return fail(WINO_E_BADARG, "direct conv: buffers (and the bias) must be 16-byte aligned");
     DtParams p;
@@ -418,7 +421,7 @@ int launch_direct_tc2(const wino_conv_desc& d, const Geometry& g, const void* x,
     const bool tf32 = d.dtype == WINO_TF32;
     const int es = tf32 ? 4 : 2;
     p.cchunks = d.c / (128 / es);
-    p.relu = d.relu; p.pool = d.pool2x2;
+    p.relu = d.relu; p.pool = d.pool2x2; p.y_nchw = 0;
     int rc = status_word(&p.status);
     if (rc) return rc;
     int bn = d.k >= 256 ? 256 : d.k >= 128 ? 128 : 64, mt = 1, resident = 0;

@@ -31,6 +31,57 @@ namespace {
 
 constexpr int DTT_W_TILE = 128 * 128;         // one tap of one chunk for this CTA's 128 filters
 
+// Stores CNT (4 or 8) consecutive outputs of one row of an NCHW plane, of which the first `left` lie inside the row
+// (pitch = row length in elements).  The element offset `off` and the pitch decide the alignment: groups of G elements
+// go out as one vector when both are multiples of G (up to 16 bytes), single elements otherwise.
+template <bool F32, int CNT>
+__device__ __forceinline__ void store_row_nchw(void* y, long long off, const float* v, int left, int pitch) {
+    const int align = (int)((off | (long long)pitch) & 7);
+    if (F32) {
+        float* dst = reinterpret_cast<float*>(y) + off;
+        const bool vec4 = (align & 3) == 0;
+#pragma unroll
+        for (int e = 0; e < CNT; e += 4) {
+            if (vec4 && e + 4 <= left) {
+                *reinterpret_cast<float4*>(dst + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (e + i < left) dst[e + i] = v[e + i];
+            }
+        }
+    } else {
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(y) + off;
+        uint32_t w[CNT / 2];
+#pragma unroll
+        for (int e = 0; e < CNT / 2; ++e) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+            w[e] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        if (CNT == 8 && align == 0 && left >= 8) {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2 % (CNT / 2)], w[3 % (CNT / 2)]);
+            return;
+        }
+        const bool vec4 = (align & 3) == 0, vec2 = (align & 1) == 0;
+#pragma unroll
+        for (int e = 0; e < CNT; e += 4) {
+            if (vec4 && e + 4 <= left) {
+                *reinterpret_cast<uint2*>(dst + e) = make_uint2(w[e / 2], w[e / 2 + 1]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; i += 2) {
+                    if (vec2 && e + i + 2 <= left) {
+                        *reinterpret_cast<uint32_t*>(dst + e + i) = w[(e + i) / 2];
+                    } else {
+                        if (e + i < left) dst[e + i] = __float2bfloat16_rn(v[e + i]);
+                        if (e + i + 1 < left) dst[e + i + 1] = __float2bfloat16_rn(v[e + i + 1]);
+                    }
+                }
+            }
+        }
+    }
+}
+
 template <int TH, int A_STAGES, int B_STAGES>
 struct DttSmem {
     static constexpr int PX_BYTES = DT_BOX_W * (TH + 2) * 128;                 // bytes one halo box brings in
@@ -202,7 +253,26 @@ direct_tc2t_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                     if (p.relu) v[e] = fmaxf(v[e], 0.f);
                 }
                 const int oy = oy0 + 2 * pr;
-                if (p.pool) {
+                if (p.y_nchw) {
+                    // NCHW: this thread's filter is a plane of y and its registers are runs of consecutive pixels of a row
+                    // (8 outputs, or 4 pooled ones): they leave as the widest vectors the row pitch keeps aligned
+                    if (k_ok) {
+                        if (p.pool) {
+                            const int py = oy >> 1;
+                            if (py < p.PH) {
+                                float m[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) m[q] = fmaxf(fmaxf(v[2 * q], v[2 * q + 1]), fmaxf(v[8 + 2 * q], v[8 + 2 * q + 1]));
+                                store_row_nchw<TF32, 4>(p.y, (((long long)n * p.K + kch) * p.PH + py) * p.PW + (ox0 >> 1), m, p.PW - (ox0 >> 1), p.PW);
+                            }
+                        } else {
+#pragma unroll
+                            for (int rr = 0; rr < 2; ++rr)
+                                if (oy + rr < p.OH)
+                                    store_row_nchw<TF32, 8>(p.y, (((long long)n * p.K + kch) * p.OH + oy + rr) * p.OW + ox0, v + 8 * rr, p.OW - ox0, p.OW);
+                        }
+                    }
+                } else if (p.pool) {
                     const int py = oy >> 1;
                     if (k_ok && py < p.PH) {
                         // element offset of the first pooled pixel of this row of windows; the others are K apart
@@ -294,7 +364,7 @@ bool direct_tc2t_applies(const wino_conv_desc& d) {
 }
 
 int launch_direct_tc2t(const wino_conv_desc& d, const Geometry& g, const void* x, const void* packed, const float* bias, void* y,
-                       cudaStream_t st) {
+                       cudaStream_t st, bool y_nchw) {
     if (d.n == 0) return WINO_OK;
     if (((uintptr_t)x | (uintptr_t)packed | (uintptr_t)y | (d.has_bias ? (uintptr_t)bias : 0)) & 15)
         return fail(WINO_E_BADARG, "direct conv: buffers (and the bias) must be 16-byte aligned");
@@ -306,7 +376,7 @@ int launch_direct_tc2t(const wino_conv_desc& d, const Geometry& g, const void* x
     p.N = d.n; p.OH = g.oh; p.OW = g.ow; p.K = d.k; p.pad = d.pad; p.PH = g.ph; p.PW = g.pw;
     p.tiles_x = (g.ow + DT_TW - 1) / DT_TW; p.tiles_y = (g.oh + th - 1) / th;
     p.cchunks = d.c / (128 / es);
-    p.relu = d.relu; p.pool = d.pool2x2;
+    p.relu = d.relu; p.pool = d.pool2x2; p.y_nchw = y_nchw ? 1 : 0;
     p.nblocks = (d.k + 255) / 256;
     p.idesc = make_idesc(tf32 ? OP_TF32 : OP_BF16, 2 * DT_TW * th, 256);
     int rc = status_word(&p.status);

@@ -11,7 +11,8 @@
 //                stack, so the classifier's FP32 GEMM reads it without a relayout or conversion pass
 //   mode 3/4     cuDNN in NCHW / NHWC: fastest forward algorithm per layer + cudnnAddTensor +
 //                cudnnActivationForward (+ cudnnPoolingForward), i.e. Network.h:171-312, :314-444
-// plus dtype=fp32|fp32x3|tf32|bf16 (default bf16), rounds= (default 10), tail=0|1.  With tail=1 the classifier tail of the
+// plus dtype=fp32|fp32x3|tf32|bf16 (default bf16), rounds= (default 10), tail=0|1, fusepool=1|0 (0: modes 0-2 run the
+// block-end pooling as its own pass, wino_maxpool2x2, the way the reference sequences it, Network.h:314-366, :603-669).  With tail=1 the classifier tail of the
 // reference (fc14 + ReLU, fc15 + ReLU, fc16, softmax, arg-max: Network.h:668-704) runs after the last round on the
 // output of conv13 (classifier_tail.h: cuBLAS GEMMs + small kernels), is checked against a host restatement for two
 // images and reports the top-1 classes.  The pretrained weights (./vggData/*.bin) and ImageNet batches the reference
@@ -35,6 +36,7 @@ int main(int argc, char** argv) {
     const int mode = (int)arg_int(argc, argv, "mode", 1);
     const int rounds = (int)arg_int(argc, argv, "rounds", 10);
     const int tail = (int)arg_int(argc, argv, "tail", 0);
+    const int fusepool = (int)arg_int(argc, argv, "fusepool", 1);
     const std::string dts = arg_str(argc, argv, "dtype", "bf16");
     const int dtype = dts == "bf16" ? WINO_BF16 : dts == "tf32" ? WINO_TF32 : dts == "fp32x3" ? WINO_FP32X3 : WINO_FP32;
     const int cudnn_dtype = dtype == WINO_FP32X3 ? WINO_FP32 : dtype;   // FP32-accurate variants face cuDNN's CUDNN_FMA_MATH
@@ -96,7 +98,7 @@ int main(int argc, char** argv) {
             memset(&d, 0, sizeof(d));
             d.layout_in = d.layout_out = layout;
             d.n = n; d.c = kVgg[l].c; d.h = d.w = kVgg[l].s; d.k = kVgg[l].k; d.pad = 1;
-            d.dtype = dtype; d.relu = 1; d.has_bias = 1; d.pool2x2 = kVgg[l].pool;
+            d.dtype = dtype; d.relu = 1; d.has_bias = 1; d.pool2x2 = kVgg[l].pool && fusepool;
             if (mode == 2 && l == 12) {        // conv13.layout_in = CHWN, layout_out = NCHW (vggCUDNN.cu:173-176)
                 d.layout_out = final_layout = WINO_NCHW;
                 if (tail) { d.out_dtype = WINO_OUT_FP32; final_dtype = dtype == WINO_BF16 ? WINO_FP32 : dtype; }
@@ -112,20 +114,28 @@ int main(int argc, char** argv) {
         for (int r = 0; r < rounds + 2; ++r) {
             HCHECK_CUDA(cudaEventRecord(e0));
             const void* cur = input;
+            int slot = 0;
             for (int l = 0; l < 13; ++l) {
-                void* out = act[l & 1];
+                void* out = act[slot];
                 HCHECK_WINO(wino_conv_forward(&desc[l], cur, u[l], (const float*)bdev[l], out, ws, wsb, nullptr));
                 cur = out;
+                slot ^= 1;
+                if (kVgg[l].pool && !fusepool) {     // the pooling pass on its own, in the layout and type the layer wrote
+                    const int pdt = desc[l].out_dtype == WINO_OUT_FP32 ? WINO_FP32 : dtype;
+                    HCHECK_WINO(wino_maxpool2x2(desc[l].layout_out, n, kVgg[l].k, kVgg[l].s, kVgg[l].s, pdt, cur, act[slot], nullptr));
+                    cur = act[slot];
+                    slot ^= 1;
+                }
             }
             HCHECK_CUDA(cudaEventRecord(e1));
             HCHECK_CUDA(cudaEventSynchronize(e1));
             float ms;
             HCHECK_CUDA(cudaEventElapsedTime(&ms, e0, e1));
             if (r >= 2) times.push_back(ms);
+            final_out = cur;
         }
         HCHECK_WINO(wino_device_status());
-        final_out = act[12 & 1];
-        what = "libwino: one fused conv+bias+ReLU(+pool) call per layer";
+        what = fusepool ? "libwino: one fused conv+bias+ReLU(+pool) call per layer" : "libwino: fused conv+bias+ReLU per layer, pooling as a separate pass";
     } else {
         cudnnHandle_t handle;
         HCHECK_CUDNN(cudnnCreate(&handle));

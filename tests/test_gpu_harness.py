@@ -69,6 +69,18 @@ def test_net_test(mode):
     assert len(re.findall(r"time:[0-9.]+ ms", out)) == 3 and s["images_per_s"] > 0
 
 
+def test_net_test_separate_pool_and_hand_off():
+    """fusepool=0 runs the block-end pooling as its own pass (the reference's sequencing); the classifier's verdict on
+    the result must be the one of the fused run.  Mode 2 also exercises the CHWN -> NCHW FP32 hand-off of conv13."""
+    tops = []
+    for fuse in (1, 0):
+        out = run("netTest", "set", "batch=2", "mode=2", "dtype=bf16", "rounds=1", "tail=1", "fusepool=%d" % fuse)
+        s = summary(out)
+        assert "classifier tail error" not in out and s["tail_top1_agree"] is True
+        tops.append(re.findall(r"Batch \d+ Resulting weights from Softmax:(\d+)", out))
+    assert tops[0] == tops[1] and len(tops[0]) == 2
+
+
 @pytest.mark.parametrize("dtype,layout,wino", [("bf16", "nhwc", 4), ("fp32", "nchw", 4), ("tf32", "chwn", 2), ("fp32x3", "nhwc", 4)])
 def test_stage_bench(dtype, layout, wino):
     """Per-stage micro-benchmark on the nine VGG-16 shapes: every staged pipeline passes its host-side check and the
