@@ -241,6 +241,7 @@ int launch_gemm_tc(int operand, const void* v, const void* u, float* m, int batc
     if ((cp * es) % 16 != 0 || kq % 4 != 0) return fail(WINO_E_BADARG, "gemm_tc: row pitch must be a multiple of 16 bytes");
     if (((uintptr_t)v | (uintptr_t)u | (uintptr_t)m) & 15) return fail(WINO_E_BADARG, "gemm_tc: buffers must be 16-byte aligned");
     static const int force_bn = [] { const char* e = getenv("WINO_GEMM_BN"); return e ? atoi(e) : 0; }();
+    if (!force_bn && gemm_tc_pair_applies(k, cp, t_rows)) return launch_gemm_tc_pair(operand, v, u, m, batches, t_rows, tp, k, cp, kq, st);
     const int bn = force_bn ? force_bn : k <= 64 ? 64 : (k >= 256 && cp >= 512) ? 256 : 128;   // long contractions: wider tiles, fewer passes over V
     const CUtensorMapDataType dt = operand_map_type(operand);
     CUtensorMap tm_v, tm_u, tm_m;

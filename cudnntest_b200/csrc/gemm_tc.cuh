@@ -11,6 +11,12 @@ namespace wino {
 int launch_gemm_tc(int operand, const void* v, const void* u, float* m, int batches, long long t_rows, long long tp,
                    int k, int cp, int kq, cudaStream_t st);
 
+// The same product on CTA pairs (tcgen05.mma.cta_group::2, 256 tiles x 256 filters per pair): gemm_tc_pair.cu.
+// launch_gemm_tc forwards to it where gemm_tc_pair_applies (wide layers; WINO_GEMM_PAIR = 0 / 1 / 2 overrides).
+bool gemm_tc_pair_applies(int k, int cp, long long t_rows);
+int launch_gemm_tc_pair(int operand, const void* v, const void* u, float* m, int batches, long long t_rows, long long tp,
+                        int k, int cp, int kq, cudaStream_t st);
+
 // Split-TF32 variant (FP32X3): V plain FP32 rows of cp floats, U rows of 2*cp floats (cp TF32 heads, then cp TF32 tails);
 // M = lo(V)*hi(U) + hi(V)*lo(U) + hi(V)*hi(U) with V split inside the kernel (gemm_tc_split.cu).
 int launch_gemm_tc_split(const float* v, const float* u, float* m, int batches, long long t_rows, long long tp, int k,

@@ -26,9 +26,13 @@ def cb():
 
 
 @pytest.mark.parametrize("dtype,operand,kind", [("tf32", 0, "tf32"), ("bf16", 1, "bf16"), ("bf16", 2, "f16")])
-@pytest.mark.parametrize("shape", [(200, 64, 64), (130, 24, 40), (1000, 256, 256), (128, 8, 200)])
+@pytest.mark.parametrize("shape", [(200, 64, 64), (130, 24, 40), (1000, 256, 256), (128, 8, 200),
+                                   (1000, 512, 256), (700, 512, 384), (300, 520, 512), (257, 1024, 264)])
 def test_tile_gemm_alone(cb, dtype, operand, kind, shape):
-    """wino_stage_gemm on random operands of the right format vs float64 GEMM of the same values."""
+    """wino_stage_gemm on random operands of the right format vs float64 GEMM of the same values.  The shapes with at
+    least 256 filters and 512 channels take the CTA-pair kernel: whole and ragged pairs of row blocks (an odd number of
+    blocks leaves one CTA of the last pair without rows), a half-empty and a barely started filter block, a contraction
+    that is not a whole number of 128-byte slices."""
     import torch
     t, c, k = shape
     # a 1-row "image" with t tiles: n = t, h = w = 2 gives one tile per image for m = 4
@@ -51,7 +55,7 @@ def test_tile_gemm_alone(cb, dtype, operand, kind, shape):
     ref = oracle.tile_gemm(v[:, :t, :c], u[:, :, :c])
     got = mm.cpu().numpy()
     assert np.isfinite(got[:, :t, :k]).all()
-    assert maxrel(got[:, :t, :k], ref) <= 2e-6
+    assert maxrel(got[:, :t, :k], ref) <= (2e-6 if c <= 512 else 4e-6)     # FP32 accumulation noise grows with the contraction length
     assert np.all(got[:, :t, k:] == 0)
 
 
