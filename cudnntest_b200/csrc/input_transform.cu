@@ -84,23 +84,30 @@ __device__ __forceinline__ void transform_words(const uint32_t* src, int row_str
 #pragma unroll
         for (int q = 0; q < A; ++q)
             w[r][q] = src[(r * row_stride + q * col_stride) * 32 + (SWZ ? (lane ^ ((r * A + q) & 31)) : 0)];
-    float d[A][A], lo[A][A], hi[A][A];
-#pragma unroll
-    for (int r = 0; r < A; ++r)
-#pragma unroll
-        for (int q = 0; q < A; ++q) d[r][q] = IO::get(w[r][q], 0);
-    input_tile_transform<A>(d, lo);
-    if (IO::VEC == 2) {
+    if constexpr (IO::VEC == 2) {
+        // two channels per word: both go through the transform together as packed FP32 pairs
+        vf2 d[A][A], o[A][A];
 #pragma unroll
         for (int r = 0; r < A; ++r)
 #pragma unroll
-            for (int q = 0; q < A; ++q) d[r][q] = IO::get(w[r][q], 1);
-        input_tile_transform<A>(d, hi);
+            for (int q = 0; q < A; ++q) d[r][q].v = make_float2(IO::get(w[r][q], 0), IO::get(w[r][q], 1));
+        input_tile_transform<A, vf2>(d, o);
+#pragma unroll
+        for (int r = 0; r < A; ++r)
+#pragma unroll
+            for (int q = 0; q < A; ++q) dst[(long long)(r * A + q) * plane_words] = IO::put(o[r][q].v.x, o[r][q].v.y);
+    } else {
+        vf1 d[A][A], o[A][A];
+#pragma unroll
+        for (int r = 0; r < A; ++r)
+#pragma unroll
+            for (int q = 0; q < A; ++q) d[r][q].v = IO::get(w[r][q], 0);
+        input_tile_transform<A, vf1>(d, o);
+#pragma unroll
+        for (int r = 0; r < A; ++r)
+#pragma unroll
+            for (int q = 0; q < A; ++q) dst[(long long)(r * A + q) * plane_words] = IO::put(o[r][q].v, 0.f);
     }
-#pragma unroll
-    for (int r = 0; r < A; ++r)
-#pragma unroll
-        for (int q = 0; q < A; ++q) dst[(long long)(r * A + q) * plane_words] = IO::put(lo[r][q], IO::VEC == 2 ? hi[r][q] : 0.f);
 }
 
 // writes element (channel c_l of the unit) of spatial position `pos` into the staged word rows
@@ -111,7 +118,7 @@ __device__ __forceinline__ void put_element(uint8_t* patch, int pos, int c_l, TI
 
 // ---- NHWC (unaligned pitch), NCHW: strip unit, cooperative loads ---------------------------------------
 template <int A, bool NCHW_IN, typename TIn, typename TOp>
-__global__ void __launch_bounds__(256, 2) input_transform_strip(const ITArgs a, const int bxchunks, const int cchunks) {
+__global__ void __launch_bounds__(256, 3) input_transform_strip(const ITArgs a, const int bxchunks, const int cchunks) {
     constexpr int M = A - 2;
     constexpr int COLS = M * IT_TX + 2;
     constexpr int VEC = 4 / (int)sizeof(TIn);
@@ -199,7 +206,7 @@ __global__ void __launch_bounds__(256, 2) input_transform_strip(const ITArgs a, 
 
 // ---- CHWN: batch unit (one tile position, 8 images), 16-byte loads along n ---------------------------------
 template <int A, typename TIn, typename TOp>
-__global__ void __launch_bounds__(256, 2) input_transform_batch(const ITArgs a, const int cchunks) {
+__global__ void __launch_bounds__(256, 3) input_transform_batch(const ITArgs a, const int cchunks) {
     constexpr int M = A - 2;
     constexpr int VEC = 4 / (int)sizeof(TIn);
     constexpr int CH = 32 * VEC;
@@ -268,11 +275,11 @@ __global__ void __launch_bounds__(256, 2) input_transform_batch(const ITArgs a, 
 }
 
 // ---- NHWC, aligned pitch: TMA-staged, persistent ------------------------------------------------------------
-constexpr int ITT_STAGES = 3;
 constexpr int ITT_WAIT_CODE = 5;
 
-template <int A, typename TIn, typename TOp>
-__global__ void __launch_bounds__(256, 2)
+// OCC resident CTAs per SM, each with a ring of ITT_STAGES patches: 3 x 2 (default) or 2 x 3 (WINO_ITT_OCC=2)
+template <int A, typename TIn, typename TOp, int OCC>
+__global__ void __launch_bounds__(256, OCC)
 input_transform_nhwc_tma(const __grid_constant__ CUtensorMap tm_x, const ITArgs a, const int bxchunks, const int cchunks,
                          const long long units, int* status) {
     constexpr int M = A - 2;
@@ -280,6 +287,7 @@ input_transform_nhwc_tma(const __grid_constant__ CUtensorMap tm_x, const ITArgs 
     constexpr int VEC = 4 / (int)sizeof(TIn);
     constexpr int CH = 32 * VEC;                       // channels per unit (128 bytes)
     constexpr int STAGE_BYTES = A * COLS * 128;
+    constexpr int ITT_STAGES = OCC == 2 ? 3 : 2;
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t ring = smem_u32(smem);
     const uint32_t bars = ring + ITT_STAGES * STAGE_BYTES;
@@ -339,12 +347,13 @@ static bool force_generic() {
     return v;
 }
 
-template <int A, typename TIn, typename TOp>
+template <int A, typename TIn, typename TOp, int OCC>
 static int run_nhwc_tma(const wino_conv_desc& d, const Geometry& g, const ITArgs& a, cudaStream_t st) {
     constexpr int M = A - 2;
     constexpr int COLS = M * IT_TX + 2;
     constexpr int VEC = 4 / (int)sizeof(TIn);
     constexpr int CH = 32 * VEC;
+    constexpr int ITT_STAGES = OCC == 2 ? 3 : 2;
     constexpr int SMEM = ITT_STAGES * A * COLS * 128 + 8 * ITT_STAGES + 16;
     CUtensorMap tm;
     const unsigned long long es = sizeof(TIn);
@@ -363,15 +372,15 @@ static int run_nhwc_tma(const wino_conv_desc& d, const Geometry& g, const ITArgs
     WINO_CUDA_CHECK(cudaGetDevice(&dev));
     cudaError_t attr_err = cudaSuccess;
     std::call_once(once[dev & 63], [&] {
-        attr_err = cudaFuncSetAttribute(input_transform_nhwc_tma<A, TIn, TOp>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        attr_err = cudaFuncSetAttribute(input_transform_nhwc_tma<A, TIn, TOp, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     });
     WINO_CUDA_CHECK(attr_err);
     const int cchunks = (g.cp + CH - 1) / CH, bxchunks = (g.bnx + IT_TX - 1) / IT_TX;
     const long long units = (long long)a.ns * g.bny * bxchunks * cchunks;
-    const long long max_ctas = 2LL * sm_count();
+    const long long max_ctas = (long long)OCC * sm_count();
     ProfScope prof(STAGE_INPUT, st);
     count_launch();
-    input_transform_nhwc_tma<A, TIn, TOp><<<(unsigned)(units < max_ctas ? units : max_ctas), 256, SMEM, st>>>(
+    input_transform_nhwc_tma<A, TIn, TOp, OCC><<<(unsigned)(units < max_ctas ? units : max_ctas), 256, SMEM, st>>>(
         tm, a, bxchunks, cchunks, units, status);
     WINO_CUDA_CHECK(cudaGetLastError());
     return WINO_OK;
@@ -380,8 +389,12 @@ static int run_nhwc_tma(const wino_conv_desc& d, const Geometry& g, const ITArgs
 template <int A, typename TIn, typename TOp>
 static int run(const wino_conv_desc& d, const Geometry& g, const ITArgs& a, cudaStream_t st) {
     constexpr int CH = 32 * (4 / (int)sizeof(TIn));
-    if (d.layout_in == WINO_NHWC && (d.c * sizeof(TIn)) % 16 == 0 && ((uintptr_t)a.x & 15) == 0 && !force_generic())
-        return run_nhwc_tma<A, TIn, TOp>(d, g, a, st);
+    if (d.layout_in == WINO_NHWC && (d.c * sizeof(TIn)) % 16 == 0 && ((uintptr_t)a.x & 15) == 0 && !force_generic()) {
+        // measured on B200 (512 -> 512 at 28 x 28, batch 256, BF16): three CTAs with two stages each 0.137 ms, two CTAs with
+        // three stages 0.147 ms: the kernel is bound by instruction latency, more resident warps help more than a deeper ring
+        static const int occ = [] { const char* e = getenv("WINO_ITT_OCC"); return e ? atoi(e) : 3; }();
+        return occ == 2 ? run_nhwc_tma<A, TIn, TOp, 2>(d, g, a, st) : run_nhwc_tma<A, TIn, TOp, 3>(d, g, a, st);
+    }
     const int cchunks = (g.cp + CH - 1) / CH;
     ProfScope prof(STAGE_INPUT, st);
     count_launch();

@@ -6,39 +6,54 @@
 
 namespace wino {
 
-// 1-D input transform t = B^T d
-template <int A>
-__device__ __forceinline__ void bt_1d(const float (&d)[A], float (&t)[A]);
+// Value types of the input transform: one float, or two floats (two channels) that go through the packed FP32
+// instructions of sm_100 (add / fma .f32x2: one issue slot for both channels, each rounded like the scalar operation).
+struct vf1 {
+    float v;
+};
+struct vf2 {
+    float2 v;
+};
+__device__ __forceinline__ vf1 vadd(vf1 a, vf1 b) { return {a.v + b.v}; }
+__device__ __forceinline__ vf1 vsub(vf1 a, vf1 b) { return {a.v - b.v}; }
+__device__ __forceinline__ vf1 vfma(float c, vf1 x, vf1 y) { return {fmaf(c, x.v, y.v)}; }            // c*x + y
+__device__ __forceinline__ vf2 vadd(vf2 a, vf2 b) { return {__fadd2_rn(a.v, b.v)}; }
+__device__ __forceinline__ vf2 vsub(vf2 a, vf2 b) { return {__ffma2_rn(make_float2(-1.f, -1.f), b.v, a.v)}; }   // exact: a - b, one rounding
+__device__ __forceinline__ vf2 vfma(float c, vf2 x, vf2 y) { return {__ffma2_rn(make_float2(c, c), x.v, y.v)}; }
 
-template <>
-__device__ __forceinline__ void bt_1d<6>(const float (&d)[6], float (&t)[6]) {
-    t[0] = 4.f * d[0] - 5.f * d[2] + d[4];
-    t[1] = -4.f * (d[1] + d[2]) + d[3] + d[4];
-    t[2] = 4.f * (d[1] - d[2]) - d[3] + d[4];
-    t[3] = -2.f * d[1] - d[2] + 2.f * d[3] + d[4];
-    t[4] = 2.f * d[1] - d[2] - 2.f * d[3] + d[4];
-    t[5] = 4.f * d[1] - 5.f * d[3] + d[5];
-}
-template <>
-__device__ __forceinline__ void bt_1d<4>(const float (&d)[4], float (&t)[4]) {
-    t[0] = d[0] - d[2];
-    t[1] = d[1] + d[2];
-    t[2] = d[2] - d[1];
-    t[3] = d[1] - d[3];
+// 1-D input transform t = B^T d (rows of B^T: comparison/wrapedConv_NCHW.cuh:836-855), 14 operations for F(4x4,3x3)
+template <int A, typename V>
+__device__ __forceinline__ void bt_1d(const V (&d)[A], V (&t)[A]) {
+    if constexpr (A == 6) {
+        const V a = vadd(d[1], d[2]), b = vadd(d[3], d[4]);
+        const V c = vsub(d[1], d[2]), e = vsub(d[4], d[3]);
+        const V f = vsub(d[3], d[1]), g = vsub(d[4], d[2]);
+        t[0] = vfma(4.f, d[0], vfma(-5.f, d[2], d[4]));
+        t[1] = vfma(-4.f, a, b);
+        t[2] = vfma(4.f, c, e);
+        t[3] = vfma(2.f, f, g);
+        t[4] = vfma(-2.f, f, g);
+        t[5] = vfma(4.f, d[1], vfma(-5.f, d[3], d[5]));
+    } else {
+        t[0] = vsub(d[0], d[2]);
+        t[1] = vadd(d[1], d[2]);
+        t[2] = vsub(d[2], d[1]);
+        t[3] = vsub(d[1], d[3]);
+    }
 }
 
 // V = B^T d B for one A x A patch held in registers (row major d[r][s]); result v[i][j]
-template <int A>
-__device__ __forceinline__ void input_tile_transform(const float (&d)[A][A], float (&v)[A][A]) {
-    float tmp[A][A];  // tmp[r][j] = sum_s d[r][s] B[s][j]
+template <int A, typename V>
+__device__ __forceinline__ void input_tile_transform(const V (&d)[A][A], V (&v)[A][A]) {
+    V tmp[A][A];  // tmp[r][j] = sum_s d[r][s] B[s][j]
 #pragma unroll
-    for (int r = 0; r < A; ++r) bt_1d<A>(d[r], tmp[r]);
+    for (int r = 0; r < A; ++r) bt_1d<A, V>(d[r], tmp[r]);
 #pragma unroll
     for (int j = 0; j < A; ++j) {
-        float col[A], out[A];
+        V col[A], out[A];
 #pragma unroll
         for (int r = 0; r < A; ++r) col[r] = tmp[r][j];
-        bt_1d<A>(col, out);
+        bt_1d<A, V>(col, out);
 #pragma unroll
         for (int i = 0; i < A; ++i) v[i][j] = out[i];
     }
