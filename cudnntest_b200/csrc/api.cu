@@ -252,7 +252,7 @@ int wino_device_status(void) {
     if (rc) return rc;
     int s = 0;
     if ((rc = read_and_clear_status(&s))) return rc;
-    if (s != 0) return fail(WINO_E_TIMEOUT, "a CTA gave up a bounded wait (code %d: tile GEMM 1 ring slot free, 2 ring slot filled, 3 accumulator drained, 4 accumulator ready; 5 input-transform patch load; 1x row-fused GEMM, 2x CTA-pair GEMM, 4x direct convolution, 90 self-test)", s);
+    if (s != 0) return fail(WINO_E_TIMEOUT, "a CTA gave up a bounded wait (code %d: tile GEMM 1 ring slot free, 2 ring slot filled, 3 accumulator drained, 4 accumulator ready; 5, 6 input-transform patch load; 1x row-fused GEMM, 2x CTA-pair GEMM, 4x direct convolution, 90 self-test)", s);
     return WINO_OK;
 }
 

@@ -16,6 +16,8 @@
 //   * NCHW: the same unit, loaded with 16-byte vectors along w (aligned chunks that cover the halo row) and
 //     scattered into the word rows; lanes run along channels so the scatter is conflict free;
 //   * CHWN: unit = one tile position x 8 images x 128 bytes of channels, loaded with 16-byte vectors along n;
+//   * NCHW and CHWN with float storage and 16-byte-aligned rows: the same units, but the patch of 32 channel planes
+//     arrives as one TMA box in persistent CTAs and is turned around inside shared memory (input_transform_planar_tma);
 //   * NHWC with an unaligned pixel pitch (C = 3, 20, ...): scalar loads, lanes along channels.
 // HBM bound: reads N*C*H*W elements (x ~1.5 through L2 for the vertical halo), writes a*a*T*Cp.
 #include <cstdlib>
@@ -274,6 +276,200 @@ __global__ void __launch_bounds__(256, 3) input_transform_batch(const ITArgs a, 
     }
 }
 
+// ---- NCHW / CHWN with 4-byte elements: TMA-staged channel planes, transposed in shared memory, persistent --------
+// The two kernels above stage a unit through registers and spend as many instructions on the gather as on the
+// transform; on B200 they reach about half of the HBM copy rate, limited by instruction latency.  For float storage
+// whose rows the TMA unit can address (every stride a multiple of 16 bytes) the gather is handed to the TMA unit:
+//   * ONE 4-D box per unit brings the patch of 32 channels in, channel-major as it lies in memory (NCHW: 32 planes of
+//     A rows x BOXW columns starting on a 16-byte boundary at or left of the patch; CHWN: 32 planes of A x A pixels x 8
+//     images); rows, columns, channels and images outside the tensor arrive as zeros (= the padding of the convolution
+//     and of V).  Boxes of the next unit are in flight while a unit is processed (ring of two);
+//   * the CTA turns the box around inside shared memory into the [position][channel] rows the transform step reads
+//     (pitch 33 words: the writes, lanes along positions, and the reads, lanes along channels, are both conflict free);
+//   * transform and store as above.
+constexpr int ITP_WAIT_CODE = 6;
+
+template <int A, bool CHWN_IN>
+struct PlanarUnit {
+    static constexpr int M = A - 2;
+    static constexpr int COLS = M * IT_TX + 2;                              // NCHW: patch columns of 8 adjacent tiles
+    static constexpr int BOXW = (COLS + 3 + 3) / 4 * 4;                     // ... covered from a 4-column boundary
+    static constexpr int POS = CHWN_IN ? A * A * IT_NB : A * COLS;          // positions the transform reads
+    static constexpr int RAW = CHWN_IN ? A * A * IT_NB : A * BOXW;          // words per channel in the box
+    static constexpr int CH = 32;
+    static constexpr int STAGES = 2;
+    static constexpr int STAGE_BYTES = CH * RAW * 4;                        // a multiple of 128
+    static constexpr int TPITCH = 33;
+    static constexpr int TBUF_BYTES = (POS * TPITCH * 4 + 127) / 128 * 128;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + TBUF_BYTES + 8 * STAGES + 16;
+    static constexpr int PER_LANE = (POS + 31) / 32;                        // positions per lane and channel in the turn-around
+};
+
+template <int A, bool CHWN_IN, typename TOp>
+__global__ void __launch_bounds__(256, 2)
+input_transform_planar_tma(const __grid_constant__ CUtensorMap tm_x, const ITArgs a, const int xchunks, const int cchunks,
+                           const long long units, int* status) {
+    using U = PlanarUnit<A, CHWN_IN>;
+    constexpr int M = U::M, COLS = U::COLS, BOXW = U::BOXW, CH = U::CH, STAGES = U::STAGES, TP = U::TPITCH;
+    extern __shared__ __align__(1024) uint8_t smem_planar[];
+    const uint32_t ring = smem_u32(smem_planar);
+    float* tbuf = reinterpret_cast<float*>(smem_planar + STAGES * U::STAGE_BYTES);
+    const uint32_t bars = ring + STAGES * U::STAGE_BYTES + U::TBUF_BYTES;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_planar + STAGES * U::STAGE_BYTES + U::TBUF_BYTES + 8 * STAGES);
+
+    const long long first = blockIdx.x;
+    const long long n_my = first < units ? (units - first + gridDim.x - 1) / gridDim.x : 0;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init(bars + 8 * s, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    // unit -> (channel chunk, x chunk, q, z); the channel chunk runs fastest so that CTAs working side by side write
+    // neighbouring 128-byte pieces of the same V rows
+    //   NCHW: xchunks = chunks of 8 tiles along x;   q = tile row by,    z = image of the slab
+    //   CHWN: xchunks = chunks of 8 images;          q = tile column bx, z = tile row by
+    auto decode = [&](long long i, int& c0, int& xc, int& q, int& z) {
+        long long u = first + i * gridDim.x;
+        c0 = (int)(u % cchunks) * CH; u /= cchunks;
+        xc = (int)(u % xchunks); u /= xchunks;
+        const int qn = CHWN_IN ? a.bnx : a.bny;
+        q = (int)(u % qn);
+        z = (int)(u / qn);
+    };
+    // first patch column of an NCHW unit rounded down to a multiple of 4 (a 16-byte boundary of the row)
+    auto box_start = [&](int xc) {
+        const int gw0 = xc * IT_TX * M - a.pad;
+        return gw0 >= 0 ? gw0 / 4 * 4 : -((-gw0 + 3) / 4 * 4);
+    };
+    auto issue = [&](long long i) {          // one thread
+        int c0, xc, q, z;
+        decode(i, c0, xc, q, z);
+        const int s = (int)(i % STAGES);
+        mbar_arrive_expect_tx(bars + 8 * s, U::STAGE_BYTES);
+        if (CHWN_IN) tma_load_4d(ring + s * U::STAGE_BYTES, &tm_x, bars + 8 * s, a.n0 + xc * IT_NB, q * M - a.pad, z * M - a.pad, c0);
+        else tma_load_4d(ring + s * U::STAGE_BYTES, &tm_x, bars + 8 * s, box_start(xc), q * M - a.pad, c0, a.n0 + z);
+    };
+    if (threadIdx.x == 0)
+        for (long long i = 0; i < n_my && i < STAGES; ++i) issue(i);
+
+    const int wv = threadIdx.x / 32, lane = threadIdx.x % 32;
+    // turn-around: warp wv moves channels 4 wv .. 4 wv + 3, lane l the positions l, l + 32, ...; the word of position p
+    // inside a channel's box does not depend on the unit (up to the NCHW column offset, which is added below)
+    int raw_of[U::PER_LANE];
+#pragma unroll
+    for (int j = 0; j < U::PER_LANE; ++j) {
+        const int p = lane + 32 * j;
+        raw_of[j] = CHWN_IN ? p : (p / COLS) * BOXW + (p % COLS);
+    }
+    const long long plane = a.tp * a.cp;
+    float* __restrict__ v = reinterpret_cast<float*>(a.v);
+    bool aborted = false;
+    for (long long i = 0; i < n_my; ++i) {
+        const int s = (int)(i % STAGES);
+        const bool ok = mbar_wait_bounded(bars + 8 * s, (uint32_t)((i / STAGES) & 1), abort_flag, status, ITP_WAIT_CODE);
+        if (!__syncthreads_and(ok)) { aborted = true; break; }
+        int c0, xc, q, z;
+        decode(i, c0, xc, q, z);
+        const float* raw = reinterpret_cast<const float*>(smem_planar + s * U::STAGE_BYTES);
+        const int off = CHWN_IN ? 0 : xc * IT_TX * M - a.pad - box_start(xc);
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+            const int c_l = 4 * wv + cc;
+#pragma unroll
+            for (int j = 0; j < U::PER_LANE; ++j) {
+                const int p = lane + 32 * j;
+                if (U::POS % 32 == 0 || p < U::POS) tbuf[p * TP + c_l] = raw[c_l * U::RAW + raw_of[j] + off];
+            }
+        }
+        __syncthreads();   // the rows are complete; the box has been read: its slot can take the unit after the next
+        if (threadIdx.x == 0 && i + STAGES < n_my) issue(i + STAGES);
+        const int c = c0 + lane;
+        long long t;
+        bool tile_ok;
+        const float* src = tbuf + lane;
+        if (CHWN_IN) {
+            const int n_l = xc * IT_NB + wv;
+            tile_ok = n_l < a.ns;
+            t = ((long long)n_l * a.bny + z) * a.bnx + q;
+            src += wv * TP;
+        } else {
+            const int bx = xc * IT_TX + wv;
+            tile_ok = bx < a.bnx;
+            t = ((long long)z * a.bny + q) * a.bnx + bx;
+            src += wv * M * TP;
+        }
+        if (tile_ok && c < a.cp) {
+            vf1 d[A][A], o[A][A];
+#pragma unroll
+            for (int r = 0; r < A; ++r)
+#pragma unroll
+                for (int s_ = 0; s_ < A; ++s_) d[r][s_].v = CHWN_IN ? src[(r * A + s_) * IT_NB * TP] : src[(r * COLS + s_) * TP];
+            input_tile_transform<A, vf1>(d, o);
+            float* dst = v + t * a.cp + c;
+#pragma unroll
+            for (int r = 0; r < A; ++r)
+#pragma unroll
+                for (int s_ = 0; s_ < A; ++s_) {
+                    *dst = to_float<TOp>(from_float<TOp>(o[r][s_].v));
+                    dst += plane;
+                }
+        }
+        __syncthreads();   // the rows are free for the next unit's turn-around
+    }
+    if (aborted && threadIdx.x == 0) drain_after_abort();
+}
+
+// float storage whose rows the TMA unit can address: base and every stride a multiple of 16 bytes, and slabs that start
+// on a 16-byte boundary of the image axis for CHWN
+static bool planar_tma_ok(const wino_conv_desc& d, const ITArgs& a) {
+    if (((uintptr_t)a.x & 15) != 0) return false;
+    if (d.layout_in == WINO_NCHW) return d.w % 4 == 0;
+    if (d.layout_in == WINO_CHWN) return d.n % 4 == 0 && a.n0 % 4 == 0;
+    return false;
+}
+
+template <int A, bool CHWN_IN, typename TOp>
+static int run_planar_tma(const wino_conv_desc& d, const Geometry& g, const ITArgs& a, cudaStream_t st) {
+    using U = PlanarUnit<A, CHWN_IN>;
+    static_assert(U::STAGE_BYTES % 128 == 0, "ring slots stay 128-byte aligned");
+    CUtensorMap tm;
+    int rc;
+    if (CHWN_IN) {
+        const unsigned long long dims[4] = {(unsigned long long)d.n, (unsigned long long)d.w, (unsigned long long)d.h, (unsigned long long)d.c};
+        const unsigned long long strides[3] = {d.n * 4ull, (unsigned long long)d.w * d.n * 4ull, (unsigned long long)d.h * d.w * d.n * 4ull};
+        const unsigned box[4] = {(unsigned)IT_NB, (unsigned)A, (unsigned)A, (unsigned)U::CH};
+        rc = encode_tensor_map(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.x, dims, strides, box, false);
+    } else {
+        const unsigned long long dims[4] = {(unsigned long long)d.w, (unsigned long long)d.h, (unsigned long long)d.c, (unsigned long long)d.n};
+        const unsigned long long strides[3] = {d.w * 4ull, (unsigned long long)d.h * d.w * 4ull, (unsigned long long)d.c * d.h * d.w * 4ull};
+        const unsigned box[4] = {(unsigned)U::BOXW, (unsigned)A, (unsigned)U::CH, 1u};
+        rc = encode_tensor_map(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.x, dims, strides, box, false);
+    }
+    if (rc) return rc;
+    int* status = nullptr;
+    if ((rc = status_word(&status))) return rc;
+    static std::once_flag once[64];
+    int dev = 0;
+    WINO_CUDA_CHECK(cudaGetDevice(&dev));
+    cudaError_t attr_err = cudaSuccess;
+    std::call_once(once[dev & 63], [&] {
+        attr_err = cudaFuncSetAttribute(input_transform_planar_tma<A, CHWN_IN, TOp>, cudaFuncAttributeMaxDynamicSharedMemorySize, U::SMEM);
+    });
+    WINO_CUDA_CHECK(attr_err);
+    const int cchunks = (g.cp + U::CH - 1) / U::CH;
+    const int xchunks = CHWN_IN ? (a.ns + IT_NB - 1) / IT_NB : (g.bnx + IT_TX - 1) / IT_TX;
+    const long long units = (long long)cchunks * xchunks * g.bny * (CHWN_IN ? g.bnx : a.ns);
+    const long long max_ctas = 2LL * sm_count();
+    ProfScope prof(STAGE_INPUT, st);
+    count_launch();
+    input_transform_planar_tma<A, CHWN_IN, TOp><<<(unsigned)(units < max_ctas ? units : max_ctas), 256, U::SMEM, st>>>(
+        tm, a, xchunks, cchunks, units, status);
+    WINO_CUDA_CHECK(cudaGetLastError());
+    return WINO_OK;
+}
+
 // ---- NHWC, aligned pitch: TMA-staged, persistent ------------------------------------------------------------
 constexpr int ITT_WAIT_CODE = 5;
 
@@ -394,6 +590,11 @@ static int run(const wino_conv_desc& d, const Geometry& g, const ITArgs& a, cuda
         // three stages 0.147 ms: the kernel is bound by instruction latency, more resident warps help more than a deeper ring
         static const int occ = [] { const char* e = getenv("WINO_ITT_OCC"); return e ? atoi(e) : 3; }();
         return occ == 2 ? run_nhwc_tma<A, TIn, TOp, 2>(d, g, a, st) : run_nhwc_tma<A, TIn, TOp, 3>(d, g, a, st);
+    }
+    if constexpr (sizeof(TIn) == 4) {
+        // float storage in NCHW / CHWN: channel planes staged by the TMA unit (WINO_GENERIC_TRANSFORMS=1 keeps the kernels below)
+        if (!force_generic() && planar_tma_ok(d, a))
+            return d.layout_in == WINO_CHWN ? run_planar_tma<A, true, TOp>(d, g, a, st) : run_planar_tma<A, false, TOp>(d, g, a, st);
     }
     const int cchunks = (g.cp + CH - 1) / CH;
     ProfScope prof(STAGE_INPUT, st);

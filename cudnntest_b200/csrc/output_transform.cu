@@ -37,39 +37,40 @@ constexpr int OT_KB = 32;
 constexpr int OT_TX = 8;
 constexpr int OT_NB = 8;
 
-// Finishes the output transform of one (tile, filter) from its products held in registers, then bias, ReLU and
-// (POOL) the 2x2 max.  ZF = false: `in` holds the a*a raw products M and both 1-D transforms run here.
+// Finishes the output transform of one (tile, filter) - or, with V = vf2, of two adjacent filters at once through the
+// packed FP32 instructions - from the products held in registers, then bias, ReLU and (POOL) the 2x2 max.
+// ZF = false: `in` holds the a*a raw products M and both 1-D transforms run here.
 // ZF = true: `in` holds Z = M A (a*m values, written by the row-fused tile GEMM) and only A^T along i is left.
 // res[p][q] holds the MO x MO stored outputs of the tile, MO = M or M/2.
-template <int A, bool POOL, bool ZF>
-__device__ __forceinline__ void finish_tile(const float (&in)[ZF ? A * (A - 2) : A * A], float b, int relu,
-                                            float (&res)[POOL ? (A - 2) / 2 : (A - 2)][POOL ? (A - 2) / 2 : (A - 2)]) {
+template <int A, bool POOL, bool ZF, typename V>
+__device__ __forceinline__ void finish_tile_v(const V (&in)[ZF ? A * (A - 2) : A * A], V b, int relu,
+                                              V (&res)[POOL ? (A - 2) / 2 : (A - 2)][POOL ? (A - 2) / 2 : (A - 2)]) {
     constexpr int M = A - 2;
-    float y[M][M];
+    V y[M][M];
     if constexpr (ZF) {
 #pragma unroll
         for (int q = 0; q < M; ++q) {
-            float col[A], out[M];
+            V col[A], out[M];
 #pragma unroll
             for (int i = 0; i < A; ++i) col[i] = in[i * M + q];
-            at_1d<A>(col, out);
+            at_1d<A, V>(col, out);
 #pragma unroll
             for (int p = 0; p < M; ++p) y[p][q] = out[p];
         }
     } else {
-        float mm[A][A];
+        V mm[A][A];
 #pragma unroll
         for (int i = 0; i < A; ++i)
 #pragma unroll
             for (int j = 0; j < A; ++j) mm[i][j] = in[i * A + j];
-        output_tile_transform<A>(mm, y);
+        output_tile_transform<A, V>(mm, y);
     }
 #pragma unroll
     for (int p = 0; p < M; ++p)
 #pragma unroll
         for (int q = 0; q < M; ++q) {
-            float v = y[p][q] + b;
-            if (relu) v = fmaxf(v, 0.f);
+            V v = vadd(y[p][q], b);
+            if (relu) v = vmax(v, vzero(v));
             y[p][q] = v;
         }
     if constexpr (POOL) {
@@ -77,13 +78,46 @@ __device__ __forceinline__ void finish_tile(const float (&in)[ZF ? A * (A - 2) :
         for (int p = 0; p < M / 2; ++p)
 #pragma unroll
             for (int q = 0; q < M / 2; ++q)
-                res[p][q] = fmaxf(fmaxf(y[2 * p][2 * q], y[2 * p][2 * q + 1]), fmaxf(y[2 * p + 1][2 * q], y[2 * p + 1][2 * q + 1]));
+                res[p][q] = vmax(vmax(y[2 * p][2 * q], y[2 * p][2 * q + 1]), vmax(y[2 * p + 1][2 * q], y[2 * p + 1][2 * q + 1]));
     } else {
 #pragma unroll
         for (int p = 0; p < M; ++p)
 #pragma unroll
             for (int q = 0; q < M; ++q) res[p][q] = y[p][q];
     }
+}
+
+// one filter, plain floats
+template <int A, bool POOL, bool ZF>
+__device__ __forceinline__ void finish_tile(const float (&in)[ZF ? A * (A - 2) : A * A], float b, int relu,
+                                            float (&res)[POOL ? (A - 2) / 2 : (A - 2)][POOL ? (A - 2) / 2 : (A - 2)]) {
+    constexpr int MO = POOL ? (A - 2) / 2 : (A - 2);
+    constexpr int P = ZF ? A * (A - 2) : A * A;
+    vf1 vin[P], vres[MO][MO];
+#pragma unroll
+    for (int i = 0; i < P; ++i) vin[i].v = in[i];
+    finish_tile_v<A, POOL, ZF, vf1>(vin, vf1{b}, relu, vres);
+#pragma unroll
+    for (int p = 0; p < MO; ++p)
+#pragma unroll
+        for (int q = 0; q < MO; ++q) res[p][q] = vres[p][q].v;
+}
+
+// two adjacent filters: in[i] = (filter k, filter k + 1)
+template <int A, bool POOL, bool ZF>
+__device__ __forceinline__ void finish_tile_pair(const float2 (&in)[ZF ? A * (A - 2) : A * A], float b0, float b1, int relu,
+                                                 float (&r0)[POOL ? (A - 2) / 2 : (A - 2)][POOL ? (A - 2) / 2 : (A - 2)],
+                                                 float (&r1)[POOL ? (A - 2) / 2 : (A - 2)][POOL ? (A - 2) / 2 : (A - 2)]) {
+    constexpr int MO = POOL ? (A - 2) / 2 : (A - 2);
+    constexpr int P = ZF ? A * (A - 2) : A * A;
+    vf2 vin[P], vres[MO][MO];
+#pragma unroll
+    for (int i = 0; i < P; ++i) vin[i].v = in[i];
+    finish_tile_v<A, POOL, ZF, vf2>(vin, vf2{make_float2(b0, b1)}, relu, vres);
+#pragma unroll
+    for (int p = 0; p < MO; ++p)
+#pragma unroll
+        for (int q = 0; q < MO; ++q) { r0[p][q] = vres[p][q].v.x; r1[p][q] = vres[p][q].v.y; }
 }
 
 // one (tile t, filter k): scalar loads, lanes along k
@@ -127,20 +161,15 @@ __global__ void __launch_bounds__(256) output_transform_direct_x2(OTArgs a, long
     const int k = (int)(item % kspan) * 2;
     const long long t = item / kspan;
     if (t >= T || k >= a.K) return;
-    float in0[P], in1[P];
+    float2 in[P];
     const long long plane = a.tp * a.kq;
     const TP* src = reinterpret_cast<const TP*>(a.m) + t * a.kq + k;
 #pragma unroll
-    for (int i = 0; i < P; ++i) {
-        const float2 v = load_pair<TP>(src + (long long)i * plane);
-        in0[i] = v.x;
-        in1[i] = v.y;
-    }
+    for (int i = 0; i < P; ++i) in[i] = load_pair<TP>(src + (long long)i * plane);
     float r0[MO][MO], r1[MO][MO];
     float b0 = 0.f, b1 = 0.f;
     if (a.bias) { b0 = __ldg(a.bias + k); b1 = __ldg(a.bias + k + 1); }
-    finish_tile<A, POOL, ZF>(in0, b0, a.relu, r0);
-    finish_tile<A, POOL, ZF>(in1, b1, a.relu, r1);
+    finish_tile_pair<A, POOL, ZF>(in, b0, b1, a.relu, r0, r1);
     const int tiles_img = a.bny * a.bnx;
     const int n = a.n0 + (int)(t / tiles_img);
     const int rem = (int)(t % tiles_img);
@@ -211,23 +240,18 @@ template <int A, bool POOL, bool ZF, typename TP, typename PosFn>
 __device__ __forceinline__ void stage_pair(const OTArgs& a, long long t, int k, int k_l, float* stage, int pitch, PosFn pos) {
     constexpr int MO = POOL ? (A - 2) / 2 : (A - 2);
     constexpr int P = ZF ? A * (A - 2) : A * A;
-    float in0[P], in1[P];
+    float2 in[P];
     const long long plane = a.tp * a.kq;
     const TP* src = reinterpret_cast<const TP*>(a.m) + t * a.kq + k;
 #pragma unroll
-    for (int i = 0; i < P; ++i) {
-        const float2 v = load_pair<TP>(src + (long long)i * plane);
-        in0[i] = v.x;
-        in1[i] = v.y;
-    }
+    for (int i = 0; i < P; ++i) in[i] = load_pair<TP>(src + (long long)i * plane);
     float r0[MO][MO], r1[MO][MO];
     float b0 = 0.f, b1 = 0.f;
     if (a.bias) {
         b0 = k < a.K ? __ldg(a.bias + k) : 0.f;
         b1 = k + 1 < a.K ? __ldg(a.bias + k + 1) : 0.f;
     }
-    finish_tile<A, POOL, ZF>(in0, b0, a.relu, r0);
-    finish_tile<A, POOL, ZF>(in1, b1, a.relu, r1);
+    finish_tile_pair<A, POOL, ZF>(in, b0, b1, a.relu, r0, r1);
 #pragma unroll
     for (int p = 0; p < MO; ++p)
 #pragma unroll

@@ -99,40 +99,52 @@ __device__ __forceinline__ void filter_tile_transform(const float (&g)[3][3], fl
     }
 }
 
-// 1-D output transform y = A^T m
-template <int A>
-__device__ __forceinline__ void at_1d(const float (&m)[A], float (&y)[A - 2]);
-
-template <>
-__device__ __forceinline__ void at_1d<6>(const float (&m)[6], float (&y)[4]) {
-    const float s12 = m[1] + m[2], d12 = m[1] - m[2];
-    const float s34 = m[3] + m[4], d34 = m[3] - m[4];
-    y[0] = m[0] + s12 + s34;
-    y[1] = d12 + 2.f * d34;
-    y[2] = s12 + 4.f * s34;
-    y[3] = d12 + 8.f * d34 + m[5];
+// 1-D output transform y = A^T m (rows of A^T: comparison/wrapedConv_NCHW.cuh:1084-1101), 10 operations for F(4x4,3x3)
+template <int A, typename V>
+__device__ __forceinline__ void at_1d(const V (&m)[A], V (&y)[A - 2]) {
+    if constexpr (A == 6) {
+        const V s12 = vadd(m[1], m[2]), d12 = vsub(m[1], m[2]);
+        const V s34 = vadd(m[3], m[4]), d34 = vsub(m[3], m[4]);
+        y[0] = vadd(vadd(m[0], s12), s34);
+        y[1] = vfma(2.f, d34, d12);
+        y[2] = vfma(4.f, s34, s12);
+        y[3] = vadd(vfma(8.f, d34, d12), m[5]);
+    } else {
+        y[0] = vadd(vadd(m[0], m[1]), m[2]);
+        y[1] = vsub(vsub(m[1], m[2]), m[3]);
+    }
 }
-template <>
-__device__ __forceinline__ void at_1d<4>(const float (&m)[4], float (&y)[2]) {
-    y[0] = m[0] + m[1] + m[2];
-    y[1] = m[1] - m[2] - m[3];
+// plain-float front end (tile GEMM epilogues)
+template <int A>
+__device__ __forceinline__ void at_1d(const float (&m)[A], float (&y)[A - 2]) {
+    vf1 mm[A], yy[A - 2];
+#pragma unroll
+    for (int i = 0; i < A; ++i) mm[i].v = m[i];
+    at_1d<A, vf1>(mm, yy);
+#pragma unroll
+    for (int i = 0; i < A - 2; ++i) y[i] = yy[i].v;
 }
 
 // Y = A^T M A for one A x A tile of products (row major mm[i][j]); result y[p][q]
-template <int A>
-__device__ __forceinline__ void output_tile_transform(const float (&mm)[A][A], float (&y)[A - 2][A - 2]) {
-    float tmp[A][A - 2];  // tmp[i][q] = sum_j mm[i][j] A[j][q]
+template <int A, typename V>
+__device__ __forceinline__ void output_tile_transform(const V (&mm)[A][A], V (&y)[A - 2][A - 2]) {
+    V tmp[A][A - 2];  // tmp[i][q] = sum_j mm[i][j] A[j][q]
 #pragma unroll
-    for (int i = 0; i < A; ++i) at_1d<A>(mm[i], tmp[i]);
+    for (int i = 0; i < A; ++i) at_1d<A, V>(mm[i], tmp[i]);
 #pragma unroll
     for (int q = 0; q < A - 2; ++q) {
-        float col[A], out[A - 2];
+        V col[A], out[A - 2];
 #pragma unroll
         for (int i = 0; i < A; ++i) col[i] = tmp[i][q];
-        at_1d<A>(col, out);
+        at_1d<A, V>(col, out);
 #pragma unroll
         for (int p = 0; p < A - 2; ++p) y[p][q] = out[p];
     }
 }
+
+__device__ __forceinline__ vf1 vmax(vf1 a, vf1 b) { return {fmaxf(a.v, b.v)}; }
+__device__ __forceinline__ vf2 vmax(vf2 a, vf2 b) { return {make_float2(fmaxf(a.v.x, b.v.x), fmaxf(a.v.y, b.v.y))}; }
+__device__ __forceinline__ vf1 vzero(vf1) { return {0.f}; }
+__device__ __forceinline__ vf2 vzero(vf2) { return {make_float2(0.f, 0.f)}; }
 
 }  // namespace wino
