@@ -115,6 +115,10 @@ __global__ void __launch_bounds__(128, 5) direct_small_c_kernel(const __grid_con
                             a.sy.n == (long long)a.oh * a.ow * a.K && k0 + 64 <= a.K &&
                             ((reinterpret_cast<uintptr_t>(a.y) | (uintptr_t)(a.K * sizeof(TOut)) | (uintptr_t)(k0 * sizeof(TOut))) & 15) == 0;
 
+    // barrier set-up and the tensor-memory allocation overlapped the previous kernel's last wave; every tensor (the
+    // packed filters too: the kernel that packs them may be the one just before this one) is touched from here on
+    pdl_launch_dependents();
+    pdl_wait();
     // filter tile: row kf = packed filter row k0 + kf (32 operand values, see pack_direct_filters), zero beyond K;
     // the bias rides in the spare contraction slot (rounded to the operand format: it is added by the MMA itself)
     if (tid < 64) {
@@ -452,7 +456,7 @@ int run(DCArgs a, cudaStream_t st) {
     }
     ProfScope prof(STAGE_DIRECT, st);
     count_launch();
-    direct_small_c_kernel<TIn, TOut, 3><<<grid, 128, 0, st>>>(tm_y, a);
+    WINO_CUDA_CHECK(launch_kernel(direct_small_c_kernel<TIn, TOut, 3>, grid, dim3(128), 0, st, pdl_enabled(), tm_y, a));
     WINO_CUDA_CHECK(cudaGetLastError());
     return WINO_OK;
 }

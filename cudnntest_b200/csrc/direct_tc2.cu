@@ -78,6 +78,8 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     cluster_sync_all();            // barriers of both CTAs initialised before any remote arrive or TMA completion
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();                    // everything above overlapped the previous kernel's last wave; tensors are touched from here on
 
     const long long tiles_img = (long long)p.tiles_x * p.tiles_y;
     const long long total_tiles = (long long)p.N * tiles_img;
@@ -377,8 +379,8 @@ int run2(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const DtParams& p, cu
     if (pairs < 1) pairs = p.nblocks;
     ProfScope prof(STAGE_DIRECT_TC, st);
     count_launch();
-    direct_tc2_kernel<BN, MT, A_STAGES, B_STAGES, B_RESIDENT, RES_CHUNKS, TF32, STG><<<(unsigned)(2 * pairs), DT_THREADS, L::TOTAL, st>>>(
-        tm_x, tm_w, tm_y ? *tm_y : tm_x, p);
+    WINO_CUDA_CHECK(launch_kernel(direct_tc2_kernel<BN, MT, A_STAGES, B_STAGES, B_RESIDENT, RES_CHUNKS, TF32, STG>, dim3((unsigned)(2 * pairs)),
+                                  dim3(DT_THREADS), L::TOTAL, st, pdl_enabled(), tm_x, tm_w, tm_y ? *tm_y : tm_x, p));
     WINO_CUDA_CHECK(cudaGetLastError());
     return WINO_OK;
 }

@@ -346,10 +346,12 @@ __global__ void __launch_bounds__(256, 2) output_transform_batch(const OTArgs a)
     TOut* __restrict__ y = (TOut*)a.y;
     const int nbase = a.n0 + nb0;
     const bool vec_ok = ((a.sy.c | a.sy.h | a.sy.w) % VE) == 0 && (nbase % VE) == 0 && (reinterpret_cast<uintptr_t>(a.y) & 15) == 0;
+    // the NVEC vectors of one (filter, pixel) - 32 contiguous bytes for float output - go to adjacent lanes, so a warp
+    // writes whole sectors
     for (int idx = threadIdx.x; idx < MO * MO * OT_KB2 * NVEC; idx += 256) {
-        const int k_l = idx % OT_KB2;
-        const int rv = idx / OT_KB2;
-        const int vec = rv % NVEC, pq = rv / NVEC;
+        const int vec = idx % NVEC;
+        const int rk = idx / NVEC;
+        const int k_l = rk % OT_KB2, pq = rk / OT_KB2;
         const int oy = by * MO + pq / MO, ox = bx * MO + pq % MO, k = k0 + k_l;
         const int n_l0 = vec * VE;
         if (oy >= a.ph || ox >= a.pw || k >= a.K || nb0 + n_l0 >= a.ns) continue;

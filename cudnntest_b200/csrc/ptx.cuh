@@ -101,6 +101,16 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+// ---- programmatic dependent launch -------------------------------------------------------------------
+// A kernel launched with the programmatic-serialisation attribute (launch_kernel below) may become resident while the
+// kernel before it in the stream is still running.  pdl_wait() blocks until that kernel has completed and its memory
+// is visible: every access to tensors (reads of x, writes of y or scratch) comes after it; what comes before it -
+// barrier set-up, tensor-memory allocation, descriptor prefetch - overlaps the predecessor's last wave.
+// pdl_launch_dependents() tells the scheduler that the next kernel may start becoming resident as this one's CTAs exit.
+// Both are no-ops in a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- CTA pairs (cluster of two) -----------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -146,6 +156,21 @@ __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap
 int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base, const unsigned long long* dims,
                       const unsigned long long* strides_bytes, const unsigned* box, bool swizzle_128);
 int sm_count();
+// true unless WINO_PDL=0: kernels that call pdl_wait() are launched with programmatic stream serialisation
+bool pdl_enabled();
+
+// kernel<<<grid, block, smem, st>>>(args...), with the programmatic-serialisation attribute when `pdl` is set.  Only for
+// kernels that execute pdl_wait() before their first access to tensors.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 // Device address of the status word the bounded waits report to (one per device, resolved once).
 int status_word(int** ptr);
 int read_and_clear_status(int* status);

@@ -1,5 +1,6 @@
 // Host-side helpers of the TMA / mbarrier kernels: tensor-map encoding through the driver entry point (no
 // link-time dependency on libcuda), SM count, and the device status word of the bounded waits.
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -88,6 +89,11 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const 
         map_cache().emplace(key, *map);
     }
     return WINO_OK;
+}
+
+bool pdl_enabled() {
+    static const bool on = [] { const char* e = getenv("WINO_PDL"); return !(e && e[0] == '0'); }();
+    return on;
 }
 
 int sm_count() {
