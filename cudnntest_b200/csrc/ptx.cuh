@@ -156,7 +156,7 @@ __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap
 int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base, const unsigned long long* dims,
                       const unsigned long long* strides_bytes, const unsigned* box, bool swizzle_128);
 int sm_count();
-// true unless WINO_PDL=0: kernels that call pdl_wait() are launched with programmatic stream serialisation
+// true with WINO_PDL=1: kernels that call pdl_wait() are then launched with programmatic stream serialisation
 bool pdl_enabled();
 
 // kernel<<<grid, block, smem, st>>>(args...), with the programmatic-serialisation attribute when `pdl` is set.  Only for
