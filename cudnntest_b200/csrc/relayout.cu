@@ -108,6 +108,35 @@ __global__ void __launch_bounds__(256) transpose_batched_vec_kernel(const uint16
     }
 }
 
+// 4-byte elements with every extent, stride and pointer a multiple of 16 bytes: 32 x 32 word tiles moved as 16-byte
+// vectors on both sides (a thread loads four consecutive q of one row and stores four consecutive r of one column);
+// the tile sits in shared memory with a pitch of 33 words, which keeps both the row-wise writes and the column-wise
+// reads conflict free.
+__global__ void __launch_bounds__(256) transpose_batched_vec4_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, int R, int Q,
+                                                                     int qtiles, long long sb_in, long long sr_in, long long sb_out,
+                                                                     long long sq_out) {
+    __shared__ uint32_t tile[32][33];
+    const int qt = blockIdx.x % qtiles;
+    const long long b = blockIdx.x / qtiles;
+    const int q0 = qt * 32, r0 = blockIdx.y * 32;
+    const int t = threadIdx.x;
+    const uint32_t* src = in + b * sb_in;
+    uint32_t* dst = out + b * sb_out;
+    {
+        const int r = t / 8, c4 = (t % 8) * 4;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r0 + r < R && q0 + c4 < Q) v = __ldg(reinterpret_cast<const uint4*>(src + (long long)(r0 + r) * sr_in + q0 + c4));
+        tile[r][c4] = v.x; tile[r][c4 + 1] = v.y; tile[r][c4 + 2] = v.z; tile[r][c4 + 3] = v.w;
+    }
+    __syncthreads();
+    {
+        const int q = t / 8, r4 = (t % 8) * 4;
+        if (q0 + q < Q && r0 + r4 < R)
+            *reinterpret_cast<uint4*>(dst + (long long)(q0 + q) * sq_out + r0 + r4) =
+                make_uint4(tile[r4][q], tile[r4 + 1][q], tile[r4 + 2][q], tile[r4 + 3][q]);
+    }
+}
+
 template <typename T>
 static int run_transpose(const void* in, void* out, long long B, long long R, long long Q, long long sb_in, long long sr_in,
                          long long sb_out, long long sq_out, cudaStream_t st) {
@@ -119,6 +148,17 @@ static int run_transpose(const void* in, void* out, long long B, long long R, lo
             count_launch();
             transpose_batched_vec_kernel<<<grid, 256, 0, st>>>((const uint16_t*)in, (uint16_t*)out, (int)R, (int)Q, (int)qt, sb_in, sr_in,
                                                                 sb_out, sq_out);
+            WINO_CUDA_CHECK(cudaGetLastError());
+            return WINO_OK;
+        }
+    }
+    if (sizeof(T) == 4 && ((R | Q | sb_in | sr_in | sb_out | sq_out) & 3) == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+        const long long qt = (Q + 31) / 32, rt = (R + 31) / 32;
+        if (B * qt <= 0x7fffffffLL && rt <= 65535 && R <= 0x7fffffffLL && Q <= 0x7fffffffLL) {
+            dim3 grid((unsigned)(B * qt), (unsigned)rt);
+            count_launch();
+            transpose_batched_vec4_kernel<<<grid, 256, 0, st>>>((const uint32_t*)in, (uint32_t*)out, (int)R, (int)Q, (int)qt, sb_in, sr_in, sb_out,
+                                                                 sq_out);
             WINO_CUDA_CHECK(cudaGetLastError());
             return WINO_OK;
         }
