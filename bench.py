@@ -46,8 +46,6 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=256, help="images per step over all GPUs (per GPU with --weak)")
     ap.add_argument("--weak", action="store_true", help="weak scaling: --batch images on every GPU")
     ap.add_argument("--wino", type=int, default=0, choices=[0, 2, 4])
-    ap.add_argument("--streams", type=int, default=1, choices=[1, 2],
-                    help="2: the two halves of a GPU's images run as two chains of layers on two streams, each filling the other's partly filled last waves")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cudnn-baseline", action="store_true", help="per-layer table without the cuDNN column")
     ap.add_argument("--no-layer-table", action="store_true", help="skip the per-layer table (ours and cuDNN) after the timed region")
@@ -205,7 +203,6 @@ def workload_config(args, world, inner, rotation=None):
                   "the 126 MB L2 or more), and every pass streams its activations (several times the L2) in between; the "
                   "end-to-end passes read inputs freshly copied from the host" % (rotation if rotation else "several"),
             "passes_per_timed_step": inner,
-            "streams_per_gpu": getattr(args, "streams", 1),
             "launch": "host launches" if getattr(args, "no_graph", False) else "one CUDA graph replay per pass"}
 
 
@@ -330,8 +327,7 @@ def run_ours(args, rank, world, local_rank):
     my_batch = hi - lo
     if my_batch <= 0:
         raise SystemExit("rank %d has no images: --batch %d is smaller than the number of GPUs" % (rank, args.batch))
-    stack = vgg.VGG16ConvStack(my_batch, layout=args.layout, dtype=args.dtype, wino=args.wino, seed=0xC0DE0040,    # same weights on every rank
-                               streams=args.streams)
+    stack = vgg.VGG16ConvStack(my_batch, layout=args.layout, dtype=args.dtype, wino=args.wino, seed=0xC0DE0040)   # same weights on every rank
     axis = shard.BATCH_AXIS[args.layout]
 
     def host_images(first, last):
@@ -508,10 +504,7 @@ def run_ours(args, rank, world, local_rank):
     # Roofline of the kernel class with the largest share of the pass.  Algorithmic bytes / flops per class come from
     # vgg.kernel_model (every layer's units summed per kernel class); the bound is whichever of bytes / HBM peak and
     # flops / tensor peak is the longer time.
-    model = vgg.kernel_model(stack.sub_batch, args.dtype, args.wino or 4, layout=args.layout, forced_wino=bool(args.wino))
-    for cls in model.values():                 # the chains of a two-stream stack each run the model of half the images
-        cls["bytes"] *= stack.streams
-        cls["flops"] *= stack.streams
+    model = vgg.kernel_model(my_batch, args.dtype, args.wino or 4, layout=args.layout, forced_wino=bool(args.wino))
     classes = {"input_transform": 0, "tile_gemm_plain": 1, "output_transform": 2, "tile_gemm_rowfused": 4, "direct_thin_input": 5,
                "direct_tensor_core": 6}
     stage = {n: {"ms": float(stage_ms[i]) / prof_passes, "launches": int(stage_n[i]) // prof_passes} for n, i in classes.items()}
@@ -573,13 +566,13 @@ def run_ours(args, rank, world, local_rank):
         out["gather"] = gather
     if world == 1 and not args.no_layer_table:
         # baselines measured in this process, outside the timed region
-        rows, err = layer_table(stack, args, stack.sub_batch)
+        rows, err = layer_table(stack, args, my_batch)
         have = [r for r in rows if r["cudnn_conv_only_ms"] is not None]
         out["baselines"] = {"cudnn": {
             "how": "torch.nn.functional.conv2d, cudnn.benchmark=True (cuDNN %s), %s, convolution alone; ours = the fused layer "
                    "(conv + bias + ReLU (+ 2x2 pool)); 10 back-to-back calls between CUDA events after 3 warm-ups"
                    % (torch.backends.cudnn.version(), "channels_last" if args.layout == "NHWC" else "NCHW"),
-            "batch": stack.sub_batch, "per_layer": rows,
+            "per_layer": rows,
             "ours_sum_ms": round(sum(r["ours_ms"] for r in rows), 4),
             "cudnn_conv_only_sum_ms": round(sum(r["cudnn_conv_only_ms"] for r in have), 4) if len(have) == len(rows) else None,
             "layers_at_or_above_cudnn": sum(1 for r in have if r["ours_over_cudnn_speed"] >= 1.0), "layers": len(rows)}}

@@ -82,101 +82,57 @@ def kernel_model(batch, dtype="bf16", wino=4, layers=VGG16_CONV, layout="NHWC", 
 
 
 class VGG16ConvStack:
-    """The 13-layer stack for a fixed batch size, layout and dtype.
-
-    streams = 2 (NCHW / NHWC, even batch) runs the two halves of the batch as two chains of layers on two CUDA streams.
-    Every kernel here is persistent and fills the GPU by itself, so the chains do not run side by side; what the second
-    chain does is occupy the SMs that the last, partly filled wave of a kernel of the first chain leaves idle (and the
-    other way round), which matters once a layer has only a few waves of work items: 32 images per GPU have 6.05 waves
-    in the 56 x 56 layers, 3.46 in the 28 x 28 layers and 0.86 in the 14 x 14 layers.  The halves share the transformed
-    filters (their format does not depend on the batch size)."""
+    """The 13-layer stack for a fixed batch size, layout and dtype."""
 
     def __init__(self, batch, layout="NHWC", dtype="bf16", wino=0, seed=0xC0DE0040, device="cuda", layers=VGG16_CONV,
-                 slab_images=0, streams=1):
+                 slab_images=0):
         self.batch, self.layout, self.dtype = batch, layout, dtype
         self.layers = list(layers)
         self.device = torch.device(device)
         self.io_dtype = torch.bfloat16 if dtype == "bf16" else torch.float32
-        if streams not in (1, 2):
-            raise ValueError("streams must be 1 or 2")
-        if streams == 2 and (layout == "CHWN" or batch % 2 or batch < 2):
-            streams = 1                      # the halves of a CHWN batch are not contiguous
-        self.streams = streams
-        self.sub_batch = batch // streams
+        ws_bytes = 0
+        for (c, k, s, pool) in self.layers:
+            d = make_desc(batch, c, s, s, k, layout, None, dtype, 1, wino, True, True, pool, 0, slab_images)
+            ws_bytes = max(ws_bytes, _lib.lib().wino_conv_workspace_bytes(ctypes.byref(d)))
+        self.workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=self.device)
         gen = torch.Generator(device="cpu").manual_seed(seed)
-        self.weights, self.biases = [], []
-        self.chains = []                     # per stream: convs, workspace, activation buffers
-        for ci in range(streams):
-            ws_bytes = 0
-            for (c, k, s, pool) in self.layers:
-                d = make_desc(self.sub_batch, c, s, s, k, layout, None, dtype, 1, wino, True, True, pool, 0, slab_images)
-                ws_bytes = max(ws_bytes, _lib.lib().wino_conv_workspace_bytes(ctypes.byref(d)))
-            workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=self.device)
-            convs, max_act = [], 0
-            for li, (c, k, s, pool) in enumerate(self.layers):
-                conv = WinoConv(self.sub_batch, c, s, s, k, layout=layout, dtype=dtype, wino=wino, relu=True, bias=True, pool=pool,
-                                slab_images=slab_images, device=device, workspace=workspace)
-                if ci == 0:
-                    w_kcrs = torch.randn((k, c, 3, 3), generator=gen) * math.sqrt(2.0 / (9 * c))
-                    b = torch.randn(k, generator=gen) * 0.01
-                    perm = {0: (0, 1, 2, 3), 1: (0, 2, 3, 1), 2: (1, 2, 3, 0)}[conv.desc.layout_in]
-                    w_l = w_kcrs.permute(perm).contiguous().to(self.io_dtype).to(self.device)
-                    b = b.to(self.device)
-                    conv.set_filter(w_l, b)
-                    self.weights.append(w_kcrs)
-                    self.biases.append(b)
-                else:                        # the same filter buffer serves both halves
-                    first = self.chains[0]["convs"][li]
-                    assert first.u_bytes == conv.u_bytes
-                    conv.u, conv.bias = first.u, first.bias
-                convs.append(conv)
-                o = s // 2 if pool else s
-                max_act = max(max_act, self.sub_batch * k * o * o)
-            act = [torch.empty(max_act, dtype=self.io_dtype, device=self.device) for _ in range(2)]
-            self.chains.append({"convs": convs, "workspace": workspace, "act": act})
-        self.convs = self.chains[0]["convs"]
-        self.act = self.chains[0]["act"]
-        self.workspace = self.chains[0]["workspace"]
+        self.convs, self.weights, self.biases = [], [], []
+        max_act = 0
+        for (c, k, s, pool) in self.layers:
+            conv = WinoConv(batch, c, s, s, k, layout=layout, dtype=dtype, wino=wino, relu=True, bias=True, pool=pool,
+                            slab_images=slab_images, device=device, workspace=self.workspace)
+            w_kcrs = torch.randn((k, c, 3, 3), generator=gen) * math.sqrt(2.0 / (9 * c))
+            b = torch.randn(k, generator=gen) * 0.01
+            perm = {0: (0, 1, 2, 3), 1: (0, 2, 3, 1), 2: (1, 2, 3, 0)}[conv.desc.layout_in]
+            w_l = w_kcrs.permute(perm).contiguous().to(self.io_dtype).to(self.device)
+            b = b.to(self.device)
+            conv.set_filter(w_l, b)
+            self.convs.append(conv)
+            self.weights.append(w_kcrs)
+            self.biases.append(b)
+            o = s // 2 if pool else s
+            max_act = max(max_act, batch * k * o * o)
+        self.act = [torch.empty(max_act, dtype=self.io_dtype, device=self.device) for _ in range(2)]
         c0, _, s0, _ = self.layers[0]
-        kl, sl, pl = self.layers[-1][1], self.layers[-1][2], self.layers[-1][3]
-        ol = sl // 2 if pl else sl
         self.in_shape = act_shape(layout, batch, c0, s0, s0)
-        self.out_shape = act_shape(layout, batch, kl, ol, ol)
-        self.side_stream = torch.cuda.Stream(device=self.device) if streams == 2 else None
-        self.out_full = torch.empty(self.out_shape, dtype=self.io_dtype, device=self.device) if streams == 2 else None
+        self.out_shape = self.convs[-1].out_shape
         self.launches_per_forward = None
-
-    def _chain_forward(self, chain, x, final_out=None):
-        cur = x
-        last = len(chain["convs"]) - 1
-        for i, conv in enumerate(chain["convs"]):
-            if i == last and final_out is not None:
-                out = final_out
-            else:
-                out = chain["act"][i % 2][: math.prod(conv.out_shape)].view(conv.out_shape)
-            conv(cur, out=out)
-            cur = out
-        return cur
 
     def forward(self, x):
         """x: input batch in `layout` (device tensor of in_shape).  Returns a view into an internal buffer."""
-        if self.streams == 1:
-            return self._chain_forward(self.chains[0], x)
-        half = self.sub_batch
-        main = torch.cuda.current_stream()
-        self.side_stream.wait_stream(main)
-        with torch.cuda.stream(self.side_stream):
-            self._chain_forward(self.chains[1], x[half:], self.out_full[half:])
-        self._chain_forward(self.chains[0], x[:half], self.out_full[:half])
-        main.wait_stream(self.side_stream)
-        return self.out_full
+        cur = x
+        for i, conv in enumerate(self.convs):
+            out = self.act[i % 2][: math.prod(conv.out_shape)].view(conv.out_shape)
+            conv(cur, out=out)
+            cur = out
+        return cur
 
     __call__ = forward
 
     def capture(self, x, prologue=None):
         """Record one forward pass over the fixed input buffer x into a CUDA graph (the 13-layer chain is short enough
         for launch gaps to show).  Runs one eager pass first: per-device set-up done on a kernel's first call cannot be
-        captured.  `prologue`, if given, is called at the head of the captured region.
+        captured.  `prologue`, if given, is called at the head of the captured region (the benchmark's L2 flush).
         Returns (graph, output view); graph.replay() recomputes the output from the current contents of x."""
         self.forward(x)
         torch.cuda.synchronize()
