@@ -135,7 +135,7 @@ def test_filters_transformed_once_serve_every_batch_size(cb, layout):
         cb.device_status()
         assert rel_l2(yb[:2], ref) <= TOL_L2
         assert rel_l2(ys, ref) <= TOL_L2
-        owner.u = torch.zeros_like(owner.u)             # a fresh buffer for the second round
+        owner.u = torch.zeros_like(owner.u)             # a fresh buffer for the other direction
 
 
 @pytest.mark.parametrize("src,dst", [("CHWN", "NCHW"), ("NHWC", "NHWC"), ("NCHW", "CHWN")])
