@@ -16,8 +16,9 @@
 //   * NCHW: the same unit, loaded with 16-byte vectors along w (aligned chunks that cover the halo row) and
 //     scattered into the word rows; lanes run along channels so the scatter is conflict free;
 //   * CHWN: unit = one tile position x 8 images x 128 bytes of channels, loaded with 16-byte vectors along n;
-//   * NCHW and CHWN with float storage and 16-byte-aligned rows: the same units, but the patch of 32 channel planes
-//     arrives as one TMA box in persistent CTAs and is turned around inside shared memory (input_transform_planar_tma);
+//   * NCHW and CHWN with 16-byte-aligned rows (every float case of the VGG shapes, bf16 NCHW with W a multiple of 8, bf16
+//     CHWN with N a multiple of 8): the same units, but the patch of channel planes arrives as one TMA box in
+//     persistent CTAs and is turned around inside shared memory (input_transform_planar_tma);
 //   * NHWC with an unaligned pixel pitch (C = 3, 20, ...): scalar loads, lanes along channels.
 // HBM bound: reads N*C*H*W elements (x ~1.5 through L2 for the vertical halo), writes a*a*T*Cp.
 #include <cstdlib>
@@ -73,10 +74,10 @@ struct WordIO<__nv_bfloat16, __half> {
     }
 };
 
-// Transforms the a x a patch whose words sit at src[(r*row_stride + s*col_stride) * 32] and stores the a*a
+// Transforms the a x a patch whose words sit at src[(r*row_stride + s*col_stride) * PITCH] and stores the a*a
 // results as words at dst[xi * plane_words].
 // SWZ: the word of lane l for patch element (r, q) sits at column l ^ (r*A + q) of its row (CHWN staging).
-template <int A, typename TIn, typename TOp, bool SWZ = false>
+template <int A, typename TIn, typename TOp, bool SWZ = false, int PITCH = 32>
 __device__ __forceinline__ void transform_words(const uint32_t* src, int row_stride, int col_stride, uint32_t* dst,
                                                 long long plane_words, int lane = 0) {
     using IO = WordIO<TIn, TOp>;
@@ -85,7 +86,7 @@ __device__ __forceinline__ void transform_words(const uint32_t* src, int row_str
     for (int r = 0; r < A; ++r)
 #pragma unroll
         for (int q = 0; q < A; ++q)
-            w[r][q] = src[(r * row_stride + q * col_stride) * 32 + (SWZ ? (lane ^ ((r * A + q) & 31)) : 0)];
+            w[r][q] = src[(r * row_stride + q * col_stride) * PITCH + (SWZ ? (lane ^ ((r * A + q) & 31)) : 0)];
     if constexpr (IO::VEC == 2) {
         // two channels per word: both go through the transform together as packed FP32 pairs
         vf2 d[A][A], o[A][A];
@@ -276,44 +277,49 @@ __global__ void __launch_bounds__(256, 3) input_transform_batch(const ITArgs a, 
     }
 }
 
-// ---- NCHW / CHWN with 4-byte elements: TMA-staged channel planes, transposed in shared memory, persistent --------
+// ---- NCHW / CHWN whose rows the TMA unit can address: channel planes staged by TMA, turned around in shared memory ----
 // The two kernels above stage a unit through registers and spend as many instructions on the gather as on the
-// transform; on B200 they reach about half of the HBM copy rate, limited by instruction latency.  For float storage
-// whose rows the TMA unit can address (every stride a multiple of 16 bytes) the gather is handed to the TMA unit:
-//   * ONE 4-D box per unit brings the patch of 32 channels in, channel-major as it lies in memory (NCHW: 32 planes of
-//     A rows x BOXW columns starting on a 16-byte boundary at or left of the patch; CHWN: 32 planes of A x A pixels x 8
-//     images); rows, columns, channels and images outside the tensor arrive as zeros (= the padding of the convolution
-//     and of V).  Boxes of the next unit are in flight while a unit is processed (ring of two);
-//   * the CTA turns the box around inside shared memory into the [position][channel] rows the transform step reads
-//     (pitch 33 words: the writes, lanes along positions, and the reads, lanes along channels, are both conflict free);
+// transform; on B200 they reach 0.41 - 0.49 of the HBM copy rate, limited by instruction latency.  Where every stride of
+// x is a multiple of 16 bytes the gather is handed to the TMA unit:
+//   * ONE 4-D box per unit brings the patch of 128 bytes' worth of channels in (32 float or 64 bf16 channels),
+//     channel-major as it lies in memory (NCHW: planes of A rows x BOXW columns starting on a 16-byte boundary at or left
+//     of the patch; CHWN: planes of A x A pixels x 8 images); rows, columns, channels and images outside the tensor
+//     arrive as zeros (= the padding of the convolution and of V).  The box of the unit after the next is in flight
+//     while a unit is processed (ring of two);
+//   * the CTA turns the box around inside shared memory into the [position][word of channels] rows the transform step
+//     reads (pitch 33 words: the writes, lanes along positions, and the reads, lanes along channels, are both conflict
+//     free; two bf16 channel planes are zipped into one word on the way);
 //   * transform and store as above.
 constexpr int ITP_WAIT_CODE = 6;
 
-template <int A, bool CHWN_IN>
+template <int A, bool CHWN_IN, typename TIn>
 struct PlanarUnit {
+    static constexpr int ES = (int)sizeof(TIn);
+    static constexpr int VEC = 4 / ES;                                      // channels per word
+    static constexpr int EPV = 16 / ES;                                     // elements per 16 bytes
     static constexpr int M = A - 2;
     static constexpr int COLS = M * IT_TX + 2;                              // NCHW: patch columns of 8 adjacent tiles
-    static constexpr int BOXW = (COLS + 3 + 3) / 4 * 4;                     // ... covered from a 4-column boundary
+    static constexpr int BOXW = (COLS + EPV - 1 + EPV - 1) / EPV * EPV;     // ... covered from a 16-byte boundary
     static constexpr int POS = CHWN_IN ? A * A * IT_NB : A * COLS;          // positions the transform reads
-    static constexpr int RAW = CHWN_IN ? A * A * IT_NB : A * BOXW;          // words per channel in the box
-    static constexpr int CH = 32;
+    static constexpr int RAW = CHWN_IN ? A * A * IT_NB : A * BOXW;          // elements per channel in the box
+    static constexpr int CH = 32 * VEC;                                     // channels per unit
     static constexpr int STAGES = 2;
-    static constexpr int STAGE_BYTES = CH * RAW * 4;                        // a multiple of 128
+    static constexpr int STAGE_BYTES = CH * RAW * ES;                       // a multiple of 128
     static constexpr int TPITCH = 33;
     static constexpr int TBUF_BYTES = (POS * TPITCH * 4 + 127) / 128 * 128;
     static constexpr int SMEM = STAGES * STAGE_BYTES + TBUF_BYTES + 8 * STAGES + 16;
-    static constexpr int PER_LANE = (POS + 31) / 32;                        // positions per lane and channel in the turn-around
+    static constexpr int PER_LANE = (POS + 31) / 32;                        // positions per lane and word in the turn-around
 };
 
-template <int A, bool CHWN_IN, typename TOp>
+template <int A, bool CHWN_IN, typename TIn, typename TOp>
 __global__ void __launch_bounds__(256, 2)
 input_transform_planar_tma(const __grid_constant__ CUtensorMap tm_x, const ITArgs a, const int xchunks, const int cchunks,
                            const long long units, int* status) {
-    using U = PlanarUnit<A, CHWN_IN>;
-    constexpr int M = U::M, COLS = U::COLS, BOXW = U::BOXW, CH = U::CH, STAGES = U::STAGES, TP = U::TPITCH;
+    using U = PlanarUnit<A, CHWN_IN, TIn>;
+    constexpr int M = U::M, COLS = U::COLS, BOXW = U::BOXW, CH = U::CH, STAGES = U::STAGES, TP = U::TPITCH, VEC = U::VEC, EPV = U::EPV;
     extern __shared__ __align__(1024) uint8_t smem_planar[];
     const uint32_t ring = smem_u32(smem_planar);
-    float* tbuf = reinterpret_cast<float*>(smem_planar + STAGES * U::STAGE_BYTES);
+    uint32_t* tbuf = reinterpret_cast<uint32_t*>(smem_planar + STAGES * U::STAGE_BYTES);
     const uint32_t bars = ring + STAGES * U::STAGE_BYTES + U::TBUF_BYTES;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_planar + STAGES * U::STAGE_BYTES + U::TBUF_BYTES + 8 * STAGES);
 
@@ -338,10 +344,10 @@ input_transform_planar_tma(const __grid_constant__ CUtensorMap tm_x, const ITArg
         q = (int)(u % qn);
         z = (int)(u / qn);
     };
-    // first patch column of an NCHW unit rounded down to a multiple of 4 (a 16-byte boundary of the row)
+    // first patch column of an NCHW unit rounded down to a 16-byte boundary of the row
     auto box_start = [&](int xc) {
         const int gw0 = xc * IT_TX * M - a.pad;
-        return gw0 >= 0 ? gw0 / 4 * 4 : -((-gw0 + 3) / 4 * 4);
+        return gw0 >= 0 ? gw0 / EPV * EPV : -((-gw0 + EPV - 1) / EPV * EPV);
     };
     auto issue = [&](long long i) {          // one thread
         int c0, xc, q, z;
@@ -355,16 +361,16 @@ input_transform_planar_tma(const __grid_constant__ CUtensorMap tm_x, const ITArg
         for (long long i = 0; i < n_my && i < STAGES; ++i) issue(i);
 
     const int wv = threadIdx.x / 32, lane = threadIdx.x % 32;
-    // turn-around: warp wv moves channels 4 wv .. 4 wv + 3, lane l the positions l, l + 32, ...; the word of position p
-    // inside a channel's box does not depend on the unit (up to the NCHW column offset, which is added below)
+    // turn-around: warp wv moves words 4 wv .. 4 wv + 3 of every position, lane l the positions l, l + 32, ...; where a
+    // position sits inside a channel's box does not depend on the unit (up to the NCHW column offset, added below)
     int raw_of[U::PER_LANE];
 #pragma unroll
     for (int j = 0; j < U::PER_LANE; ++j) {
         const int p = lane + 32 * j;
         raw_of[j] = CHWN_IN ? p : (p / COLS) * BOXW + (p % COLS);
     }
-    const long long plane = a.tp * a.cp;
-    float* __restrict__ v = reinterpret_cast<float*>(a.v);
+    const long long plane_words = a.tp * a.cp / VEC;
+    uint32_t* __restrict__ vw = reinterpret_cast<uint32_t*>(a.v);
     bool aborted = false;
     for (long long i = 0; i < n_my; ++i) {
         const int s = (int)(i % STAGES);
@@ -372,23 +378,31 @@ input_transform_planar_tma(const __grid_constant__ CUtensorMap tm_x, const ITArg
         if (!__syncthreads_and(ok)) { aborted = true; break; }
         int c0, xc, q, z;
         decode(i, c0, xc, q, z);
-        const float* raw = reinterpret_cast<const float*>(smem_planar + s * U::STAGE_BYTES);
         const int off = CHWN_IN ? 0 : xc * IT_TX * M - a.pad - box_start(xc);
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
-            const int c_l = 4 * wv + cc;
+            const int w_l = 4 * wv + cc;
 #pragma unroll
             for (int j = 0; j < U::PER_LANE; ++j) {
                 const int p = lane + 32 * j;
-                if (U::POS % 32 == 0 || p < U::POS) tbuf[p * TP + c_l] = raw[c_l * U::RAW + raw_of[j] + off];
+                if (U::POS % 32 == 0 || p < U::POS) {
+                    uint32_t word;
+                    if constexpr (VEC == 1) {
+                        word = reinterpret_cast<const uint32_t*>(smem_planar + s * U::STAGE_BYTES)[w_l * U::RAW + raw_of[j] + off];
+                    } else {
+                        const unsigned short* raw = reinterpret_cast<const unsigned short*>(smem_planar + s * U::STAGE_BYTES);
+                        word = (uint32_t)raw[(2 * w_l) * U::RAW + raw_of[j] + off] | ((uint32_t)raw[(2 * w_l + 1) * U::RAW + raw_of[j] + off] << 16);
+                    }
+                    tbuf[p * TP + w_l] = word;
+                }
             }
         }
         __syncthreads();   // the rows are complete; the box has been read: its slot can take the unit after the next
         if (threadIdx.x == 0 && i + STAGES < n_my) issue(i + STAGES);
-        const int c = c0 + lane;
+        const int c = c0 + lane * VEC;
         long long t;
         bool tile_ok;
-        const float* src = tbuf + lane;
+        const uint32_t* src = tbuf + lane;
         if (CHWN_IN) {
             const int n_l = xc * IT_NB + wv;
             tile_ok = n_l < a.ns;
@@ -400,52 +414,42 @@ input_transform_planar_tma(const __grid_constant__ CUtensorMap tm_x, const ITArg
             t = ((long long)z * a.bny + q) * a.bnx + bx;
             src += wv * M * TP;
         }
-        if (tile_ok && c < a.cp) {
-            vf1 d[A][A], o[A][A];
-#pragma unroll
-            for (int r = 0; r < A; ++r)
-#pragma unroll
-                for (int s_ = 0; s_ < A; ++s_) d[r][s_].v = CHWN_IN ? src[(r * A + s_) * IT_NB * TP] : src[(r * COLS + s_) * TP];
-            input_tile_transform<A, vf1>(d, o);
-            float* dst = v + t * a.cp + c;
-#pragma unroll
-            for (int r = 0; r < A; ++r)
-#pragma unroll
-                for (int s_ = 0; s_ < A; ++s_) {
-                    *dst = to_float<TOp>(from_float<TOp>(o[r][s_].v));
-                    dst += plane;
-                }
-        }
+        if (tile_ok && c < a.cp)
+            transform_words<A, TIn, TOp, false, TP>(src, CHWN_IN ? A * IT_NB : COLS, CHWN_IN ? IT_NB : 1, vw + (t * a.cp + c) / VEC, plane_words);
         __syncthreads();   // the rows are free for the next unit's turn-around
     }
     if (aborted && threadIdx.x == 0) drain_after_abort();
 }
 
-// float storage whose rows the TMA unit can address: base and every stride a multiple of 16 bytes, and slabs that start
-// on a 16-byte boundary of the image axis for CHWN
+// storage whose rows the TMA unit can address: base and every stride a multiple of 16 bytes, and slabs that start on a
+// 16-byte boundary of the image axis for CHWN
+template <typename TIn>
 static bool planar_tma_ok(const wino_conv_desc& d, const ITArgs& a) {
+    constexpr int EPV = 16 / (int)sizeof(TIn);
     if (((uintptr_t)a.x & 15) != 0) return false;
-    if (d.layout_in == WINO_NCHW) return d.w % 4 == 0;
-    if (d.layout_in == WINO_CHWN) return d.n % 4 == 0 && a.n0 % 4 == 0;
+    if (d.layout_in == WINO_NCHW) return d.w % EPV == 0;
+    if (d.layout_in == WINO_CHWN) return d.n % EPV == 0 && a.n0 % EPV == 0;
     return false;
 }
 
-template <int A, bool CHWN_IN, typename TOp>
+template <int A, bool CHWN_IN, typename TIn, typename TOp>
 static int run_planar_tma(const wino_conv_desc& d, const Geometry& g, const ITArgs& a, cudaStream_t st) {
-    using U = PlanarUnit<A, CHWN_IN>;
+    using U = PlanarUnit<A, CHWN_IN, TIn>;
     static_assert(U::STAGE_BYTES % 128 == 0, "ring slots stay 128-byte aligned");
+    const CUtensorMapDataType dt = sizeof(TIn) == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    const unsigned long long es = sizeof(TIn);
     CUtensorMap tm;
     int rc;
     if (CHWN_IN) {
         const unsigned long long dims[4] = {(unsigned long long)d.n, (unsigned long long)d.w, (unsigned long long)d.h, (unsigned long long)d.c};
-        const unsigned long long strides[3] = {d.n * 4ull, (unsigned long long)d.w * d.n * 4ull, (unsigned long long)d.h * d.w * d.n * 4ull};
+        const unsigned long long strides[3] = {d.n * es, (unsigned long long)d.w * d.n * es, (unsigned long long)d.h * d.w * d.n * es};
         const unsigned box[4] = {(unsigned)IT_NB, (unsigned)A, (unsigned)A, (unsigned)U::CH};
-        rc = encode_tensor_map(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.x, dims, strides, box, false);
+        rc = encode_tensor_map(&tm, dt, 4, a.x, dims, strides, box, false);
     } else {
         const unsigned long long dims[4] = {(unsigned long long)d.w, (unsigned long long)d.h, (unsigned long long)d.c, (unsigned long long)d.n};
-        const unsigned long long strides[3] = {d.w * 4ull, (unsigned long long)d.h * d.w * 4ull, (unsigned long long)d.c * d.h * d.w * 4ull};
+        const unsigned long long strides[3] = {d.w * es, (unsigned long long)d.h * d.w * es, (unsigned long long)d.c * d.h * d.w * es};
         const unsigned box[4] = {(unsigned)U::BOXW, (unsigned)A, (unsigned)U::CH, 1u};
-        rc = encode_tensor_map(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.x, dims, strides, box, false);
+        rc = encode_tensor_map(&tm, dt, 4, a.x, dims, strides, box, false);
     }
     if (rc) return rc;
     int* status = nullptr;
@@ -455,7 +459,7 @@ static int run_planar_tma(const wino_conv_desc& d, const Geometry& g, const ITAr
     WINO_CUDA_CHECK(cudaGetDevice(&dev));
     cudaError_t attr_err = cudaSuccess;
     std::call_once(once[dev & 63], [&] {
-        attr_err = cudaFuncSetAttribute(input_transform_planar_tma<A, CHWN_IN, TOp>, cudaFuncAttributeMaxDynamicSharedMemorySize, U::SMEM);
+        attr_err = cudaFuncSetAttribute(input_transform_planar_tma<A, CHWN_IN, TIn, TOp>, cudaFuncAttributeMaxDynamicSharedMemorySize, U::SMEM);
     });
     WINO_CUDA_CHECK(attr_err);
     const int cchunks = (g.cp + U::CH - 1) / U::CH;
@@ -464,7 +468,7 @@ static int run_planar_tma(const wino_conv_desc& d, const Geometry& g, const ITAr
     const long long max_ctas = 2LL * sm_count();
     ProfScope prof(STAGE_INPUT, st);
     count_launch();
-    input_transform_planar_tma<A, CHWN_IN, TOp><<<(unsigned)(units < max_ctas ? units : max_ctas), 256, U::SMEM, st>>>(
+    input_transform_planar_tma<A, CHWN_IN, TIn, TOp><<<(unsigned)(units < max_ctas ? units : max_ctas), 256, U::SMEM, st>>>(
         tm, a, xchunks, cchunks, units, status);
     WINO_CUDA_CHECK(cudaGetLastError());
     return WINO_OK;
@@ -591,11 +595,9 @@ static int run(const wino_conv_desc& d, const Geometry& g, const ITArgs& a, cuda
         static const int occ = [] { const char* e = getenv("WINO_ITT_OCC"); return e ? atoi(e) : 3; }();
         return occ == 2 ? run_nhwc_tma<A, TIn, TOp, 2>(d, g, a, st) : run_nhwc_tma<A, TIn, TOp, 3>(d, g, a, st);
     }
-    if constexpr (sizeof(TIn) == 4) {
-        // float storage in NCHW / CHWN: channel planes staged by the TMA unit (WINO_GENERIC_TRANSFORMS=1 keeps the kernels below)
-        if (!force_generic() && planar_tma_ok(d, a))
-            return d.layout_in == WINO_CHWN ? run_planar_tma<A, true, TOp>(d, g, a, st) : run_planar_tma<A, false, TOp>(d, g, a, st);
-    }
+    // NCHW / CHWN whose rows the TMA unit can address: channel planes staged by TMA (WINO_GENERIC_TRANSFORMS=1 keeps the kernels below)
+    if (!force_generic() && planar_tma_ok<TIn>(d, a))
+        return d.layout_in == WINO_CHWN ? run_planar_tma<A, true, TIn, TOp>(d, g, a, st) : run_planar_tma<A, false, TIn, TOp>(d, g, a, st);
     const int cchunks = (g.cp + CH - 1) / CH;
     ProfScope prof(STAGE_INPUT, st);
     count_launch();
