@@ -238,21 +238,27 @@ direct_tc2t_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             const float bias = (p.bias && kch < p.K) ? __ldg(p.bias + kch) : 0.f;
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * NCOL) + who * NPIX;
             const int oy0 = ty * TH, ox0 = tx * DT_TW;
+            // lanes 2j and 2j+1 hold neighbouring filters: in the unpooled NHWC store the even lane takes the upper pixel
+            // row of a step for both filters and the odd lane the lower one, so that every store is one 4- or 8-byte word
+            const int odd = lane & 1;
+            const int nvalid = min(8, p.OW - ox0);
+            uint32_t r[16];
+            tmem_ld_32x16(lane_addr, r);
 #pragma unroll 1
             for (int pr = 0; pr < TH / 2; ++pr) {     // two pixel rows (16 columns) per step: one row of 2x2 pool windows
-                uint32_t r[16];
-                tmem_ld_32x16(lane_addr + pr * 16, r);
                 tmem_ld_wait();
-                if (pr == TH / 2 - 1) {               // accumulator stage drained: release it on the leader
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * as);
-                }
                 float v[16];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
                     v[e] = __uint_as_float(r[e]) + bias;
                     if (p.relu) v[e] = fmaxf(v[e], 0.f);
+                }
+                if (pr == TH / 2 - 1) {               // accumulator stage drained: release it on the leader
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * as);
+                } else {
+                    tmem_ld_32x16(lane_addr + (pr + 1) * 16, r);    // in flight while this step's values leave
                 }
                 const int oy = oy0 + 2 * pr;
                 if (p.y_nchw) {
@@ -288,18 +294,30 @@ direct_tc2t_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                             }
                         }
                     }
-                } else if (k_ok) {
+                } else {
+                    // K is a multiple of 16: both lanes of a pair are inside K together, and the shuffles run on every lane
+                    const int row = oy + odd;
+                    const bool st_ok = k_ok && row < p.OH;
+                    const long long o0 = (((long long)n * p.OH + row) * p.OW + ox0) * p.K + (kch & ~1);
+                    if (TF32) {
+                        float* dst = reinterpret_cast<float*>(p.y) + o0;
 #pragma unroll
-                    for (int rr = 0; rr < 2; ++rr) {
-                        if (oy + rr < p.OH) {
-                            const long long o0 = (((long long)n * p.OH + oy + rr) * p.OW + ox0) * p.K + kch;
+                        for (int e = 0; e < 8; ++e) {
+                            const float keep = odd ? v[8 + e] : v[e];
+                            const float recv = __shfl_xor_sync(0xffffffffu, odd ? v[e] : v[8 + e], 1);
+                            if (st_ok && e < nvalid)
+                                *reinterpret_cast<float2*>(dst + (long long)e * p.K) = odd ? make_float2(recv, keep) : make_float2(keep, recv);
+                        }
+                    } else {
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.y) + o0;
+                        const uint32_t sel = odd ? 0x3276u : 0x5410u;
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                if (ox0 + e < p.OW) {
-                                    if (TF32) reinterpret_cast<float*>(p.y)[o0 + e * p.K] = v[8 * rr + e];
-                                    else reinterpret_cast<__nv_bfloat16*>(p.y)[o0 + e * p.K] = __float2bfloat16_rn(v[8 * rr + e]);
-                                }
-                            }
+                        for (int e = 0; e < 8; ++e) {
+                            const __nv_bfloat162 both = __floats2bfloat162_rn(v[e], v[8 + e]);     // low half: upper row
+                            const uint32_t own = *reinterpret_cast<const uint32_t*>(&both);
+                            const uint32_t recv = __shfl_xor_sync(0xffffffffu, own, 1);
+                            if (st_ok && e < nvalid)
+                                *reinterpret_cast<uint32_t*>(dst + (long long)e * p.K) = __byte_perm(own, recv, sel);
                         }
                     }
                 }
