@@ -173,7 +173,8 @@ def test_direct_tensor_core_path(cb, shape, pool):
 
 
 @pytest.mark.parametrize("shape,pool", [((2, 64, 32, 24, 64), True), ((1, 128, 20, 20, 128), False), ((3, 32, 17, 13, 80), True),
-                                        ((2, 256, 16, 24, 256), True), ((1, 96, 9, 9, 64), False), ((1, 64, 12, 12, 512), False)])
+                                        ((2, 256, 16, 24, 256), True), ((1, 96, 9, 9, 64), False), ((1, 64, 12, 12, 512), False),
+                                        ((1, 64, 7, 9, 256), False)])
 @pytest.mark.parametrize("layout", ["NHWC", "NCHW", "CHWN"])
 def test_direct_tensor_core_path_tf32(cb, shape, pool, layout):
     """Float storage with TF32 operands: C a multiple of 32 (up to 256) and K a multiple of 16 run the CTA-pair
