@@ -28,6 +28,32 @@ namespace wino {
 
 namespace {
 
+// 2x2 max-pool across the lanes of a warp whose lane index is 8 * (pixel row) + (pixel column) of a tile.  A full
+// butterfly (every lane exchanges every word with lane ^ 1, then lane ^ 8) costs two shuffles per word and leaves the
+// same result in four lanes; here each exchange also halves what a lane keeps: the odd column keeps the upper half of
+// the words, the odd row the upper half of what is left.  3/4 of a shuffle per word, and every lane ends with
+// WORDS / 4 results: words [first, first + WORDS / 4) of the window's pooled values, first = pooled_first_word().
+// Shuffles share the shared-memory data path with the MMA's operand reads, which is what this kernel is short of.
+template <int WORDS, typename Op>
+__device__ __forceinline__ void pool2x2_split(uint32_t (&w)[WORDS], int lane, Op op) {
+    constexpr int H = WORDS / 2, Q = WORDS / 4;
+    const bool oddx = lane & 1, oddy = lane & 8;
+#pragma unroll
+    for (int i = 0; i < H; ++i) {
+        const uint32_t keep = oddx ? w[H + i] : w[i];
+        const uint32_t got = __shfl_xor_sync(0xffffffffu, oddx ? w[i] : w[H + i], 1);
+        w[i] = op(keep, got);
+    }
+#pragma unroll
+    for (int i = 0; i < Q; ++i) {
+        const uint32_t keep = oddy ? w[Q + i] : w[i];
+        const uint32_t got = __shfl_xor_sync(0xffffffffu, oddy ? w[i] : w[Q + i], 8);
+        w[i] = op(keep, got);
+    }
+}
+template <int WORDS>
+__device__ __forceinline__ int pooled_first_word(int lane) { return ((lane & 1) ? WORDS / 2 : 0) + ((lane & 8) ? WORDS / 4 : 0); }
+
 template <int BN, int MT, int A_STAGES, int B_STAGES, bool B_RESIDENT, int RES_CHUNKS, bool STG = false>
 struct Dt2Smem {
     static constexpr int B_TILE = (BN / 2) * 128;          // this CTA's half of one tap of one 64-channel chunk
@@ -216,6 +242,10 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         uint32_t aphase = 0;
         bool ok = true;
         [[maybe_unused]] bool stg_pending = false;
+        // With one 32-filter chunk per warp the bias of that chunk stays in registers while the filter block does not
+        // change (for resident filters: the whole kernel); eight 16-byte loads per accumulator tile otherwise.
+        [[maybe_unused]] float4 bias_r[8];
+        [[maybe_unused]] int bias_k0 = -1;
         for (long long u = first; ok && u < total; u += step) {
             if (!mbar_wait_bounded(bar_tfull + 8 * as, aphase, abort_flag, p.status, DT_W_T_FULL)) ok = false;
             ok = __all_sync(0xffffffffu, ok);
@@ -230,7 +260,7 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 bool writer;
                 long long pix;
                 if (p.pool) {
-                    writer = valid && ((ph_ | pw_) & 1) == 0 && (oy >> 1) < p.PH && (ox >> 1) < p.PW;
+                    writer = valid && (oy >> 1) < p.PH && (ox >> 1) < p.PW;      // each lane of a window stores a quarter of its filters
                     pix = ((long long)n * p.PH + (oy >> 1)) * p.PW + (ox >> 1);
                 } else {
                     writer = valid && oy < p.OH && ox < p.OW;
@@ -247,13 +277,26 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * as);
                     }
                     const int k0 = nb * BN + half * (BN / 2) + chunk * 32;
+                    auto load_bias4 = [&](int e) {
+                        return (p.bias && k0 + e + 4 <= p.K) ? __ldg(reinterpret_cast<const float4*>(p.bias + k0 + e)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    };
+                    if constexpr (CHUNKS == 1) {
+                        if (k0 != bias_k0) {
+#pragma unroll
+                            for (int e = 0; e < 32; e += 4) bias_r[e / 4] = load_bias4(e);
+                            bias_k0 = k0;
+                        }
+                    }
+                    auto bias4 = [&](int e) {
+                        if constexpr (CHUNKS == 1) return bias_r[e / 4];
+                        else return load_bias4(e);
+                    };
                     if constexpr (TF32) {
                         // float storage: bias + ReLU, the 2x2 max with two shuffles per value, 16-byte stores
                         float v[32];
 #pragma unroll
                         for (int e = 0; e < 32; e += 4) {
-                            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (p.bias && k0 + e + 4 <= p.K) b4 = __ldg(reinterpret_cast<const float4*>(p.bias + k0 + e));
+                            const float4 b4 = bias4(e);
                             v[e] = __uint_as_float(r[e]) + b4.x; v[e + 1] = __uint_as_float(r[e + 1]) + b4.y;
                             v[e + 2] = __uint_as_float(r[e + 2]) + b4.z; v[e + 3] = __uint_as_float(r[e + 3]) + b4.w;
                         }
@@ -262,13 +305,23 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                             for (int e = 0; e < 32; ++e) v[e] = fmaxf(v[e], 0.f);
                         }
                         if (p.pool) {
+                            uint32_t u[32];
 #pragma unroll
-                            for (int e = 0; e < 32; ++e) {
-                                v[e] = fmaxf(v[e], __shfl_xor_sync(0xffffffffu, v[e], 1));
-                                v[e] = fmaxf(v[e], __shfl_xor_sync(0xffffffffu, v[e], 8));
+                            for (int e = 0; e < 32; ++e) u[e] = __float_as_uint(v[e]);
+                            pool2x2_split<32>(u, lane, [](uint32_t a, uint32_t b) { return __float_as_uint(fmaxf(__uint_as_float(a), __uint_as_float(b))); });
+                            if (writer) {
+                                const int f0 = pooled_first_word<32>(lane);          // this lane's 8 filters of the chunk
+                                float* dst = reinterpret_cast<float*>(p.y) + pix * p.K + k0 + f0;
+                                if (k0 + 32 <= p.K && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                                    reinterpret_cast<uint4*>(dst)[0] = make_uint4(u[0], u[1], u[2], u[3]);
+                                    reinterpret_cast<uint4*>(dst)[1] = make_uint4(u[4], u[5], u[6], u[7]);
+                                } else {
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e)
+                                        if (k0 + f0 + e < p.K) dst[e] = __uint_as_float(u[e]);
+                                }
                             }
-                        }
-                        if (writer) {
+                        } else if (writer) {
                             float* dst = reinterpret_cast<float*>(p.y) + pix * p.K + k0;
                             if (k0 + 32 <= p.K && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
@@ -284,8 +337,7 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     uint32_t w[16];
 #pragma unroll
                     for (int e = 0; e < 32; e += 4) {
-                        float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (p.bias && k0 + e + 4 <= p.K) b4 = __ldg(reinterpret_cast<const float4*>(p.bias + k0 + e));
+                        const float4 b4 = bias4(e);
                         float v0 = __uint_as_float(r[e]) + b4.x, v1 = __uint_as_float(r[e + 1]) + b4.y;
                         float v2 = __uint_as_float(r[e + 2]) + b4.z, v3 = __uint_as_float(r[e + 3]) + b4.w;
                         if (p.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); v2 = fmaxf(v2, 0.f); v3 = fmaxf(v3, 0.f); }
@@ -294,17 +346,22 @@ direct_tc2_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         w[e / 2 + 1] = *reinterpret_cast<uint32_t*>(&h1);
                     }
                     if (p.pool) {
+                        pool2x2_split<16>(w, lane, [](uint32_t a, uint32_t b) {
+                            const __nv_bfloat162 m = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+                            return *reinterpret_cast<const uint32_t*>(&m);
+                        });
+                        if (writer) {
+                            const int f0 = 2 * pooled_first_word<16>(lane);          // this lane's 8 filters of the chunk
+                            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.y) + pix * p.K + k0 + f0;
+                            if (k0 + 32 <= p.K && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                                *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                            } else {
 #pragma unroll
-                        for (int e = 0; e < 16; ++e) {
-                            uint32_t o = __shfl_xor_sync(0xffffffffu, w[e], 1);
-                            __nv_bfloat162 m = __hmax2(*reinterpret_cast<__nv_bfloat162*>(&w[e]), *reinterpret_cast<__nv_bfloat162*>(&o));
-                            uint32_t mu = *reinterpret_cast<uint32_t*>(&m);
-                            o = __shfl_xor_sync(0xffffffffu, mu, 8);
-                            m = __hmax2(m, *reinterpret_cast<__nv_bfloat162*>(&o));
-                            w[e] = *reinterpret_cast<uint32_t*>(&m);
+                                for (int e = 0; e < 8; ++e)
+                                    if (k0 + f0 + e < p.K) dst[e] = reinterpret_cast<const __nv_bfloat16*>(w)[e];
+                            }
                         }
-                    }
-                    if (STG && !p.pool) {
+                    } else if (STG) {
                         // Unpooled outputs leave through the TMA unit: the warp lays its 32 pixels x 64 filters out as a
                         // 128-byte-swizzled box (8 wide, 4 high) in its own staging tile and one lane stores it; the
                         // box is clipped at the image and filter edges.  Stored from registers instead, every 16-byte
