@@ -391,10 +391,21 @@ int wino_conv_forward(const wino_conv_desc* d, const void* x, const void* u, con
     void* v = (void*)base;
     void* prod = (void*)(base + v_bytes(g, tp));
     cudaStream_t st = (cudaStream_t)stream;
+    // Wide tensor-core layers with an NHWC result: the raw products cross HBM in 3 bytes instead of 4 (they fit the same
+    // buffer).  Decided once per call from the whole batch, so that the result does not depend on the slab size; it
+    // needs nothing from the filter buffer.
+    const bool m24 = g.prod_kind == 0 && gemm_tc_m24_applies(g.operand, d->k, g.cp, g.kq, (long long)d->n * g.tiles_img) &&
+                     output_transform_m24_ok(*d, y) && (long long)g.a * g.a * tp * g.kq * 2 < (1LL << 32);
     for (int n0 = 0; n0 < d->n; n0 += ns) {
         const int cur = d->n - n0 < ns ? d->n - n0 : ns;
         if ((rc = launch_input_transform(*d, g, x, n0, cur, v, tp, st))) return rc;
-        if ((rc = run_conv_gemm(g, v, u, prod, d->k, (long long)cur * g.tiles_img, tp, st))) return rc;
+        const long long t_rows = (long long)cur * g.tiles_img;
+        if (m24) {
+            if ((rc = launch_gemm_tc_pair(g.operand, v, u, (float*)prod, g.a * g.a, t_rows, tp, d->k, g.cp, g.kq, st, true))) return rc;
+            if ((rc = launch_output_transform(*d, g, prod, 3, bias, y, n0, cur, tp, st))) return rc;
+            continue;
+        }
+        if ((rc = run_conv_gemm(g, v, u, prod, d->k, t_rows, tp, st))) return rc;
         if ((rc = launch_output_transform(*d, g, prod, g.prod_kind, bias, y, n0, cur, tp, st))) return rc;
     }
     return WINO_OK;

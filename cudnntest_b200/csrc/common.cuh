@@ -156,9 +156,11 @@ struct ProfScope {
 int launch_filter_transform(const wino_conv_desc& d, const Geometry& g, const void* w, void* u, cudaStream_t st);
 int launch_input_transform(const wino_conv_desc& d, const Geometry& g, const void* x, int n0, int ns, void* v,
                            long long tp, cudaStream_t st);
-// prod_kind: 0 = raw products M[a*a] (float), 1 = row-transformed Z[a*m] (float), 2 = Z (half)
+// prod_kind: 0 = raw products M[a*a] (float), 1 = row-transformed Z[a*m] (float), 2 = Z (half), 3 = raw products in
+// 3 bytes (plane of upper 16 bits at m, plane of third bytes behind it; NHWC destinations: output_transform_m24_ok)
 int launch_output_transform(const wino_conv_desc& d, const Geometry& g, const void* m, int prod_kind, const float* bias,
                             void* y, int n0, int ns, long long tp, cudaStream_t st);
+bool output_transform_m24_ok(const wino_conv_desc& d, const void* y);
 int launch_gemm_ffma(const float* v, const float* u, float* m, int batches, long long t_rows, long long tp, int k,
                      int cp, int kq, cudaStream_t st);
 // direct convolution on tensor cores for thin, large-spatial NHWC BF16 layers, C = 64 / 128 (direct_tc.cu)

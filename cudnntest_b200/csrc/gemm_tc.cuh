@@ -15,7 +15,10 @@ int launch_gemm_tc(int operand, const void* v, const void* u, float* m, int batc
 // launch_gemm_tc forwards to it where gemm_tc_pair_applies (wide layers; WINO_GEMM_PAIR = 0 / 1 / 2 overrides).
 bool gemm_tc_pair_applies(int k, int cp, long long t_rows);
 int launch_gemm_tc_pair(int operand, const void* v, const void* u, float* m, int batches, long long t_rows, long long tp,
-                        int k, int cp, int kq, cudaStream_t st);
+                        int k, int cp, int kq, cudaStream_t st, bool m24 = false);
+// 3-byte products (upper 24 bits of each float, as a 16-bit plane and a byte plane): where the pair kernel applies,
+// WINO_M24=0 disables
+bool gemm_tc_m24_applies(int operand, int k, int cp, int kq, long long t_rows);
 
 // Split-TF32 variant (FP32X3): V plain FP32 rows of cp floats, U rows of 2*cp floats (cp TF32 heads, then cp TF32 tails);
 // M = lo(V)*hi(U) + hi(V)*lo(U) + hi(V)*hi(U) with V split inside the kernel (gemm_tc_split.cu).

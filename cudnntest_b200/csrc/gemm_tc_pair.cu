@@ -48,21 +48,27 @@ struct TpParams {
     int* status;
 };
 
-template <int STAGES>
+constexpr int TP_STORE_TILE24 = 32 * 128 + 32 * 64;   // 3-byte products: 32 rows x 64 upper halves + 32 rows x 64 third bytes
+
+template <int STAGES, bool M24 = false>
 struct TpSmem {
     static constexpr int A_OFF = 0;
     static constexpr int B_OFF = STAGES * TC_A_BYTES;
-    static constexpr int STORE_OFF = B_OFF + STAGES * TP_B_BYTES;          // 4 warps x 2 staging tiles of 4 KiB
-    static constexpr int BAR_OFF = STORE_OFF + 2 * TP_EPI_WARPS * TP_STORE_TILE;   // full[STAGES], empty[STAGES], tfull[2], tempty[2]
+    static constexpr int STORE_OFF = B_OFF + STAGES * TP_B_BYTES;          // 4 warps x 2 staging tiles of 4 (6) KiB
+    static constexpr int STORE_TILE = M24 ? TP_STORE_TILE24 : TP_STORE_TILE;
+    static constexpr int BAR_OFF = STORE_OFF + 2 * TP_EPI_WARPS * STORE_TILE;   // full[STAGES], empty[STAGES], tfull[2], tempty[2]
     static constexpr int SLOT_OFF = BAR_OFF + 8 * (2 * STAGES + 4);
     static constexpr int TOTAL = SLOT_OFF + 16 + 1024;
 };
 
-template <bool TF32, int STAGES>
+// M24: the products leave as the upper 24 bits of each float (rounded to nearest), split into a plane of 16-bit upper
+// halves (tm_m) and a plane of third bytes (tm_lo): 3 bytes per product through HBM instead of 4, and again when the
+// output transform reads them.
+template <bool TF32, int STAGES, bool M24>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TP_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_u,
-                    const __grid_constant__ CUtensorMap tm_m, const TpParams p) {
-    using L = TpSmem<STAGES>;
+                    const __grid_constant__ CUtensorMap tm_m, const __grid_constant__ CUtensorMap tm_lo, const TpParams p) {
+    using L = TpSmem<STAGES, M24>;
     constexpr int ESIZE = TF32 ? 4 : 2;
     constexpr int KC = TC_ROW_BYTES / ESIZE;        // contraction elements per ring slot
     constexpr int UMMA_K = 32 / ESIZE;              // contraction elements per tcgen05.mma
@@ -160,8 +166,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
         }
     } else {
         const int quarter = warp % 4;                 // tensor-memory lanes [32*quarter, 32*quarter + 32)
-        uint8_t* stage_gen = gen_base + L::STORE_OFF + quarter * 2 * TP_STORE_TILE;
-        const uint32_t stage_s = base + L::STORE_OFF + quarter * 2 * TP_STORE_TILE;
+        uint8_t* stage_gen = gen_base + L::STORE_OFF + quarter * 2 * L::STORE_TILE;
+        const uint32_t stage_s = base + L::STORE_OFF + quarter * 2 * L::STORE_TILE;
         const uint32_t tempty_leader = mapa_shared(bar_tempty, 0);
         int as = 0;
         uint32_t aphase = 0, issued = 0;
@@ -174,6 +180,57 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
             if (!ok) break;
             tc_fence_after();
             const long long row0 = (long long)(mp * 2 + (int)rank) * TC_BM + quarter * 32;
+            if constexpr (M24) {
+#pragma unroll 1
+                for (int unit = 0; unit < TP_BN / 64; ++unit) {       // 64 columns at a time
+                    uint32_t r[64];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * TP_BN + unit * 64);
+                    tmem_ld_32x32(taddr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+                    tmem_ld_32x32(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+                    tmem_ld_wait();
+                    if (unit == TP_BN / 64 - 1) {     // this warp's share of the accumulator is in registers
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(tempty_leader + 8 * as);
+                    }
+                    const int col0 = nb * TP_BN + unit * 64;
+                    if (row0 < p.t_rows && col0 < p.kq) {
+                        const uint32_t buf = issued & 1;
+                        if (issued >= 2) {            // the stores that last used this staging tile must have read it
+                            if (lane == 0) tma_store_wait_read<1>();
+                            __syncwarp();
+                        }
+#pragma unroll
+                        for (int i = 0; i < 64; ++i) r[i] += 0x80u;       // round the 24 kept bits to nearest
+                        // upper halves: 64 x 2 bytes per row, 128-byte swizzle (16-byte chunk index XOR row mod 8)
+                        uint4* hi = reinterpret_cast<uint4*>(stage_gen + buf * L::STORE_TILE + lane * 128);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            hi[j ^ (lane & 7)] = make_uint4(__byte_perm(r[8 * j], r[8 * j + 1], 0x7632), __byte_perm(r[8 * j + 2], r[8 * j + 3], 0x7632),
+                                                            __byte_perm(r[8 * j + 4], r[8 * j + 5], 0x7632), __byte_perm(r[8 * j + 6], r[8 * j + 7], 0x7632));
+                        // third bytes: 64 bytes per row, 64-byte swizzle (chunk index XOR (row / 2) mod 4)
+                        uint4* lo = reinterpret_cast<uint4*>(stage_gen + buf * L::STORE_TILE + 32 * 128 + lane * 64);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const uint32_t* q = &r[16 * j + 4 * e];
+                                w[e] = __byte_perm(__byte_perm(q[0], q[1], 0x0051), __byte_perm(q[2], q[3], 0x0051), 0x5410);
+                            }
+                            lo[j ^ ((lane >> 1) & 3)] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                        fence_async_shared();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_3d(&tm_m, stage_s + buf * L::STORE_TILE, col0, (int)row0, xi);
+                            tma_store_3d(&tm_lo, stage_s + buf * L::STORE_TILE + 32 * 128, col0, (int)row0, xi);
+                            tma_store_commit();
+                        }
+                        ++issued;
+                    }
+                }
+            } else {
 #pragma unroll 1
             for (int chunk = 0; chunk < TP_BN / 32; ++chunk) {
                 uint32_t r[32];
@@ -205,6 +262,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
                     ++issued;
                 }
             }
+            }
             as ^= 1;
             if (as == 0) aphase ^= 1;
         }
@@ -221,16 +279,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_v, const __grid_const
     }
 }
 
-template <bool TF32, int STAGES>
-int run(const CUtensorMap& tm_v, const CUtensorMap& tm_u, const CUtensorMap& tm_m, const TpParams& p, cudaStream_t st) {
-    using L = TpSmem<STAGES>;
+template <bool TF32, int STAGES, bool M24>
+int run(const CUtensorMap& tm_v, const CUtensorMap& tm_u, const CUtensorMap& tm_m, const CUtensorMap& tm_lo, const TpParams& p,
+        cudaStream_t st) {
+    using L = TpSmem<STAGES, M24>;
     static_assert(L::TOTAL <= 232448, "shared memory budget of one CTA exceeded");
     static std::once_flag once[64];
     int dev = 0;
     WINO_CUDA_CHECK(cudaGetDevice(&dev));
     cudaError_t attr_err = cudaSuccess;
     std::call_once(once[dev & 63], [&] {
-        attr_err = cudaFuncSetAttribute(gemm_tc_pair_kernel<TF32, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        attr_err = cudaFuncSetAttribute(gemm_tc_pair_kernel<TF32, STAGES, M24>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     });
     WINO_CUDA_CHECK(attr_err);
     const long long total = (long long)p.batches * p.mpairs * p.nblocks;
@@ -239,7 +298,7 @@ int run(const CUtensorMap& tm_v, const CUtensorMap& tm_u, const CUtensorMap& tm_
     if (pairs < 1) pairs = 1;
     ProfScope prof(STAGE_GEMM, st);
     count_launch();
-    gemm_tc_pair_kernel<TF32, STAGES><<<(unsigned)(2 * pairs), TP_THREADS, L::TOTAL, st>>>(tm_v, tm_u, tm_m, p);
+    gemm_tc_pair_kernel<TF32, STAGES, M24><<<(unsigned)(2 * pairs), TP_THREADS, L::TOTAL, st>>>(tm_v, tm_u, tm_m, tm_lo, p);
     WINO_CUDA_CHECK(cudaGetLastError());
     return WINO_OK;
 }
@@ -258,8 +317,16 @@ bool gemm_tc_pair_applies(int k, int cp, long long t_rows) {
     return mode >= 2 || cp >= 512;
 }
 
+// 3-byte products: for layers the pair kernel takes, filters padded to a multiple of 16 (the row pitch of the byte plane)
+bool gemm_tc_m24_applies(int operand, int k, int cp, int kq, long long t_rows) {
+    static const bool off = [] { const char* e = getenv("WINO_M24"); return e && e[0] == '0'; }();
+    static const bool bn_forced = [] { const char* e = getenv("WINO_GEMM_BN"); return e && atoi(e) > 0; }();
+    return !off && !bn_forced && (operand == OP_TF32 || operand == OP_BF16 || operand == OP_F16) && kq % 16 == 0 &&
+           gemm_tc_pair_applies(k, cp, t_rows);
+}
+
 int launch_gemm_tc_pair(int operand, const void* v, const void* u, float* m, int batches, long long t_rows, long long tp,
-                        int k, int cp, int kq, cudaStream_t st) {
+                        int k, int cp, int kq, cudaStream_t st, bool m24) {
     if (t_rows <= 0) return WINO_OK;
     if (operand != OP_TF32 && operand != OP_BF16 && operand != OP_F16)
         return fail(WINO_E_BADARG, "gemm_tc_pair: bad operand kind %d", operand);
@@ -271,7 +338,20 @@ int launch_gemm_tc_pair(int operand, const void* v, const void* u, float* m, int
     int rc;
     if ((rc = make_map_k128(&tm_v, dt, es, v, cp, t_rows, tp, batches, TC_BM))) return rc;
     if ((rc = make_map_k128(&tm_u, dt, es, u, cp, k, k, batches, TP_BN / 2))) return rc;
-    if ((rc = make_map_k128(&tm_m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, m, kq, t_rows, tp, batches, 32))) return rc;
+    CUtensorMap tm_lo;
+    if (m24) {
+        if (kq % 16 != 0) return fail(WINO_E_BADARG, "gemm_tc_pair: 3-byte products need a filter pitch that is a multiple of 16");
+        // plane of upper halves: [batches][tp][kq] 16-bit, boxes of 64 x 32; plane of third bytes behind it, 64-byte swizzle
+        if ((rc = make_map_k128(&tm_m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, m, kq, t_rows, tp, batches, 32))) return rc;
+        const unsigned long long dims[3] = {(unsigned long long)kq, (unsigned long long)t_rows, (unsigned long long)batches};
+        const unsigned long long strides[2] = {(unsigned long long)kq, (unsigned long long)tp * kq};
+        const unsigned box[3] = {64u, 32u, 1u};
+        const char* lo_plane = reinterpret_cast<const char*>(m) + (long long)batches * tp * kq * 2;
+        if ((rc = encode_tensor_map(&tm_lo, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, lo_plane, dims, strides, box, 2))) return rc;
+    } else {
+        if ((rc = make_map_k128(&tm_m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, m, kq, t_rows, tp, batches, 32))) return rc;
+        tm_lo = tm_m;
+    }
     TpParams p;
     p.t_rows = t_rows; p.cp = cp; p.kq = kq; p.batches = batches;
     const long long mblocks = (t_rows + TC_BM - 1) / TC_BM;
@@ -280,7 +360,8 @@ int launch_gemm_tc_pair(int operand, const void* v, const void* u, float* m, int
     p.kchunks = (cp * es + TC_ROW_BYTES - 1) / TC_ROW_BYTES;
     p.idesc = make_idesc(operand, TP_BN, 2 * TC_BM);
     if ((rc = status_word(&p.status))) return rc;
-    return operand == OP_TF32 ? run<true, 5>(tm_v, tm_u, tm_m, p, st) : run<false, 5>(tm_v, tm_u, tm_m, p, st);
+    if (m24) return operand == OP_TF32 ? run<true, 5, true>(tm_v, tm_u, tm_m, tm_lo, p, st) : run<false, 5, true>(tm_v, tm_u, tm_m, tm_lo, p, st);
+    return operand == OP_TF32 ? run<true, 5, false>(tm_v, tm_u, tm_m, tm_lo, p, st) : run<false, 5, false>(tm_v, tm_u, tm_m, tm_lo, p, st);
 }
 
 }  // namespace wino

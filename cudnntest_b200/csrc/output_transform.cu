@@ -13,6 +13,8 @@
 //     contiguous along w;
 //   * CHWN: one tile position x 8 images x 32 filters are staged and written contiguous along n.
 // HBM bound: reads a*a*T*K floats, writes N*K*OH*OW elements (a quarter of that with the pool).
+#include <type_traits>
+
 #include "common.cuh"
 #include "wino_math.cuh"
 
@@ -20,6 +22,7 @@ namespace wino {
 
 struct OTArgs {
     const void* m;       // products M[a*a][tp][kq] (float) or row-transformed Z[a*m][tp][kq] (float / half)
+    const void* m_lo;    // 3-byte products: plane of the third bytes (m is then the plane of the upper 16 bits)
     const float* bias;
     void* y;
     int K;
@@ -140,6 +143,19 @@ __device__ __forceinline__ float2 load_pair<float>(const float* p) { return *rei
 template <>
 __device__ __forceinline__ float2 load_pair<__half>(const __half* p) { return __half22float2(*reinterpret_cast<const __half2*>(p)); }
 
+// Raw products stored in 3 bytes: the upper 24 bits of the float (sign, exponent, 15 mantissa bits; the tile GEMM rounds
+// to nearest), as one plane of 16-bit upper halves and one plane of third bytes with the same [a*a][tp][kq] indexing.
+struct m24_t { unsigned short hi; };
+__device__ __forceinline__ float2 load_pair_m24(const unsigned short* hi, const unsigned char* lo) {
+    const uint32_t h = *reinterpret_cast<const uint32_t*>(hi);
+    const uint32_t l = *reinterpret_cast<const unsigned short*>(lo);
+    // float 0: bytes (0, lo.b0, hi.b0, hi.b1); float 1: bytes (0, lo.b1, hi.b2, hi.b3); selector 4 picks l.b0, 5 l.b1
+    // (selector 7 is the top byte of the zero-extended 16-bit load: the low byte of each float is 0)
+    const uint32_t f0 = __byte_perm(h, l, 0x1047);
+    const uint32_t f1 = __byte_perm(h, l, 0x3257);
+    return make_float2(__uint_as_float(f0), __uint_as_float(f1));
+}
+
 template <typename T>
 __device__ __forceinline__ void store_pair(T* p, float a, float b);
 template <>
@@ -163,9 +179,19 @@ __global__ void __launch_bounds__(256) output_transform_direct_x2(OTArgs a, long
     if (t >= T || k >= a.K) return;
     float2 in[P];
     const long long plane = a.tp * a.kq;
-    const TP* src = reinterpret_cast<const TP*>(a.m) + t * a.kq + k;
+    if constexpr (std::is_same<TP, m24_t>::value) {
+        // both planes are below 4 GiB (the launcher checks): 32-bit offsets from the two plane bases
+        const unsigned char* __restrict__ hi = reinterpret_cast<const unsigned char*>(a.m);
+        const unsigned char* __restrict__ lo = reinterpret_cast<const unsigned char*>(a.m_lo);
+        const unsigned off0 = (unsigned)(t * a.kq + k), pl = (unsigned)plane;
 #pragma unroll
-    for (int i = 0; i < P; ++i) in[i] = load_pair<TP>(src + (long long)i * plane);
+        for (int i = 0; i < P; ++i)
+            in[i] = load_pair_m24(reinterpret_cast<const unsigned short*>(hi + 2u * (off0 + (unsigned)i * pl)), lo + (off0 + (unsigned)i * pl));
+    } else {
+        const TP* src = reinterpret_cast<const TP*>(a.m) + t * a.kq + k;
+#pragma unroll
+        for (int i = 0; i < P; ++i) in[i] = load_pair<TP>(src + (long long)i * plane);
+    }
     float r0[MO][MO], r1[MO][MO];
     float b0 = 0.f, b1 = 0.f;
     if (a.bias) { b0 = __ldg(a.bias + k); b1 = __ldg(a.bias + k + 1); }
@@ -399,7 +425,31 @@ static int dispatch(const wino_conv_desc& d, const Geometry& g, const OTArgs& a,
     return bf16 ? run<A, false, ZF, TP, __nv_bfloat16>(d, g, a, st) : run<A, false, ZF, TP, float>(d, g, a, st);
 }
 
-// prod_kind: 0 = raw products M (float), 1 = row-transformed Z (float), 2 = row-transformed Z (half)
+// 3-byte products exist for the NHWC two-filters-per-thread kernel only (the caller checks output_transform_m24_ok)
+template <int A>
+static int run_m24(const wino_conv_desc& d, const Geometry& g, const OTArgs& a, cudaStream_t st) {
+    ProfScope prof(STAGE_OUTPUT, st);
+    count_launch();
+    const long long T = (long long)a.ns * g.tiles_img;
+    const long long items = T * (((d.k / 2) + 31) / 32 * 32);
+    const unsigned blocks = (unsigned)((items + 255) / 256);
+    const bool bf16 = g.out_bf16 != 0;
+    if (d.pool2x2) {
+        if (bf16) output_transform_direct_x2<A, true, false, m24_t, __nv_bfloat16><<<blocks, 256, 0, st>>>(a, T);
+        else output_transform_direct_x2<A, true, false, m24_t, float><<<blocks, 256, 0, st>>>(a, T);
+    } else {
+        if (bf16) output_transform_direct_x2<A, false, false, m24_t, __nv_bfloat16><<<blocks, 256, 0, st>>>(a, T);
+        else output_transform_direct_x2<A, false, false, m24_t, float><<<blocks, 256, 0, st>>>(a, T);
+    }
+    WINO_CUDA_CHECK(cudaGetLastError());
+    return WINO_OK;
+}
+
+bool output_transform_m24_ok(const wino_conv_desc& d, const void* y) {
+    return d.layout_out == WINO_NHWC && d.k % 2 == 0 && ((uintptr_t)y & 7) == 0;
+}
+
+// prod_kind: 0 = raw products M (float), 1 = row-transformed Z (float), 2 = row-transformed Z (half), 3 = raw products in 3 bytes (two planes)
 int launch_output_transform(const wino_conv_desc& d, const Geometry& g, const void* m, int prod_kind, const float* bias,
                             void* y, int n0, int ns, long long tp, cudaStream_t st) {
     if (ns <= 0) return WINO_OK;
@@ -407,7 +457,7 @@ int launch_output_transform(const wino_conv_desc& d, const Geometry& g, const vo
         return fail(WINO_E_UNSUPPORTED, "output transform: slab of %d images / %dx%d tiles exceeds the grid limits", ns,
                     g.bny, g.bnx);
     OTArgs a;
-    a.m = m; a.bias = d.has_bias ? bias : nullptr; a.y = y; a.K = d.k;
+    a.m = m; a.m_lo = nullptr; a.bias = d.has_bias ? bias : nullptr; a.y = y; a.K = d.k;
     a.oh = g.oh; a.ow = g.ow; a.ph = g.ph; a.pw = g.pw;
     a.n0 = n0; a.ns = ns; a.bny = g.bny; a.bnx = g.bnx; a.kq = g.kq; a.tp = tp;
     a.relu = d.relu; a.pool = d.pool2x2;
@@ -415,6 +465,14 @@ int launch_output_transform(const wino_conv_desc& d, const Geometry& g, const vo
     if (prod_kind == 0) return g.a == 6 ? dispatch<6, false, float>(d, g, a, st) : dispatch<4, false, float>(d, g, a, st);
     if (prod_kind == 1) return g.a == 6 ? dispatch<6, true, float>(d, g, a, st) : dispatch<4, true, float>(d, g, a, st);
     if (prod_kind == 2) return g.a == 6 ? dispatch<6, true, __half>(d, g, a, st) : dispatch<4, true, __half>(d, g, a, st);
+    if (prod_kind == 3) {
+        if (!output_transform_m24_ok(d, y) || ((uintptr_t)m & 15))
+            return fail(WINO_E_BADARG, "output transform: 3-byte products need an NHWC destination and an even filter count");
+        if ((long long)g.a * g.a * tp * g.kq * 2 >= (1LL << 32))
+            return fail(WINO_E_UNSUPPORTED, "output transform: 3-byte product planes are limited to 4 GiB per slab");
+        a.m_lo = (const char*)m + (long long)g.a * g.a * tp * g.kq * 2;
+        return g.a == 6 ? run_m24<6>(d, g, a, st) : run_m24<4>(d, g, a, st);
+    }
     return fail(WINO_E_BADARG, "output transform: bad product kind %d", prod_kind);
 }
 

@@ -152,9 +152,9 @@ __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap
 
 // ---- host side (tma_host.cu) ---------------------------------------------------------------------------
 // Encodes a tiled tensor map.  dims / box are innermost first; strides_bytes has rank-1 entries (dimension 0 is
-// dense).  swizzle_128: 128-byte swizzle (inner box extent must be 128 bytes), else none.
+// dense).  swizzle: 0 = none, 1 (true) = 128-byte swizzle (inner box extent 128 bytes), 2 = 64-byte swizzle (64 bytes).
 int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base, const unsigned long long* dims,
-                      const unsigned long long* strides_bytes, const unsigned* box, bool swizzle_128);
+                      const unsigned long long* strides_bytes, const unsigned* box, int swizzle);
 int sm_count();
 // true with WINO_PDL=1: kernels that call pdl_wait() are then launched with programmatic stream serialisation
 bool pdl_enabled();

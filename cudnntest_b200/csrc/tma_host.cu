@@ -61,13 +61,13 @@ int* g_status_ptr[kMaxDevices] = {nullptr};
 }  // namespace
 
 int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base, const unsigned long long* dims,
-                      const unsigned long long* strides_bytes, const unsigned* box, bool swizzle_128) {
+                      const unsigned long long* strides_bytes, const unsigned* box, int swizzle) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(WINO_E_CUDA, "cuTensorMapEncodeTiled entry point not available");
     if (rank < 1 || rank > 5) return fail(WINO_E_BADARG, "tensor map rank %d", rank);
     MapKey key;
     memset(&key, 0, sizeof(key));
-    key.base = (unsigned long long)(uintptr_t)base; key.dt = (int)dt; key.rank = rank; key.swizzle = swizzle_128 ? 1 : 0;
+    key.base = (unsigned long long)(uintptr_t)base; key.dt = (int)dt; key.rank = rank; key.swizzle = swizzle;
     for (int i = 0; i < rank; ++i) { key.dims[i] = dims[i]; key.box[i] = box[i]; }
     for (int i = 0; i + 1 < rank; ++i) key.strides[i] = strides_bytes[i];
     {
@@ -80,7 +80,7 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const 
     for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; e[i] = 1; }
     for (int i = 0; i + 1 < rank; ++i) s[i] = strides_bytes[i];
     CUresult r = fn(map, dt, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    swizzle_128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(WINO_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     {

@@ -271,3 +271,24 @@ def test_vgg16_stack_layer_by_layer_and_graph(cb):
     cb.device_status()
     assert torch.equal(y, eager)
     assert stack.launches_per_forward >= 13
+
+
+@pytest.mark.parametrize("case", [
+    # n, c, h, w, k, dtype, layout_in, pool, slab_images
+    (8, 512, 28, 28, 512, "bf16", "NHWC", False, 0),
+    (8, 512, 28, 28, 512, "bf16", "NHWC", True, 0),
+    (20, 512, 14, 14, 272, "bf16", "NHWC", False, 0),       # a ragged 256-filter block, a ragged pair of row blocks
+    (40, 512, 12, 12, 256, "bf16", "NCHW", True, 32),       # two slabs, the second one less than one row block of tiles
+    (12, 512, 20, 20, 512, "tf32", "NHWC", False, 0),
+    (16, 512, 13, 17, 256, "tf32", "CHWN", True, 0),
+])
+def test_three_byte_products(cb, case):
+    """Wide tensor-core layers with an NHWC result move the raw products M between the CTA-pair tile GEMM and the output
+    transform as the upper 24 bits of each float (a 16-bit plane and a byte plane): the forced Winograd pipeline against
+    the oracle, whole and ragged tiles, both output element types, several slabs."""
+    n, c, h, w, k, dtype, layout, pool, slab = case
+    x, wt, b = make_inputs(n, c, h, w, k, seed=n + h + k)
+    y = run_conv(x, wt, b, layout, layout_out="NHWC", dtype=dtype, relu=True, pool=pool, wino=4, slab_images=slab)
+    ref = oracle.conv_f64(x, wt, b, pad=1, relu=True, pool=pool)
+    assert y.shape == ref.shape
+    assert rel_l2(y, ref) <= TOL_L2
