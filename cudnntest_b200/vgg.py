@@ -49,7 +49,8 @@ def kernel_model(batch, dtype="bf16", wino=4, layers=VGG16_CONV, layout="NHWC", 
     """Algorithmic bytes and flops of one forward pass per kernel class, following the engine's per-layer choice
     for NHWC: C <= 3 (no pool): thin-input direct kernel; BF16 with C a multiple of 64 and (C <= 256, an image
     smaller than 28 x 28 or fewer than 128 * 784 pixels in the batch): direct tensor-core kernel; other tensor-core layers with C <= 128: row-fused tile GEMM
-    (products Z, a*m planes, half for bf16); otherwise the plain tile GEMM (products M, a*a float planes)."""
+    (products Z, a*m planes, half for bf16); otherwise the plain tile GEMM (products M, a*a planes of floats, or of 3-byte values where the CTA-pair kernel
+    writes them for an NHWC result)."""
     a, m = wino + 2, wino
     s_io = 2 if dtype == "bf16" else 4
     out = {k: {"bytes": 0, "flops": 0} for k in ("input_transform", "tile_gemm_plain", "tile_gemm_rowfused",
@@ -72,7 +73,10 @@ def kernel_model(batch, dtype="bf16", wino=4, layers=VGG16_CONV, layout="NHWC", 
         split = dtype == "fp32x3"      # V stays plain FP32 and is split into TF32 head + tail inside the tile GEMM
         v_bytes = a * a * tiles * cp * s_io
         fused = dtype in ("tf32", "bf16") and c <= 128
-        p_bytes = (a * m * tiles * kq * (2 if dtype == "bf16" else 4)) if fused else a * a * tiles * kq * 4
+        # wide tensor-core layers with an NHWC result move the raw products in 3 bytes (CTA-pair tile GEMM, csrc/gemm_tc_pair.cu)
+        m24 = (not fused and dtype in ("tf32", "bf16") and layout == "NHWC" and k >= 256 and k % 2 == 0 and cp >= 512 and
+               kq % 16 == 0 and tiles >= 256)
+        p_bytes = (a * m * tiles * kq * (2 if dtype == "bf16" else 4)) if fused else a * a * tiles * kq * (3 if m24 else 4)
         out["input_transform"]["bytes"] += batch * c * s * s * s_io + v_bytes
         g = out["tile_gemm_rowfused" if fused else "tile_gemm_plain"]
         g["bytes"] += v_bytes + p_bytes
