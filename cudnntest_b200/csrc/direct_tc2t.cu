@@ -12,10 +12,14 @@
 //     read as the N-side operand whose rows are split between the two CTAs: each CTA loads and holds its own box;
 //   * the filter operand is a plain 128-row K-major tile per tap and chunk, streamed through a TMA ring;
 //   * epilogue: a thread owns one filter (accumulator lane) and reads the pixels of one of the pair's two tiles from
-//     tensor memory, 16 columns (two pixel rows) at a time.  The bias is one scalar per thread, the 2x2 max-pool is
-//     taken inside the thread's registers, and a warp's 32 lanes store 32 consecutive NHWC channels of a pixel
-//     (64 contiguous bytes for BF16).  With at least two 64-channel chunks per work item the MMAs take several times
-//     longer than this drain, which runs underneath them on the other accumulator stage.
+//     tensor memory, 16 columns (two pixel rows) at a time, the next load in flight while a step's values leave.  The
+//     bias is one scalar per thread, the 2x2 max-pool is taken inside the thread's registers, and a warp's 32 lanes
+//     store 32 consecutive NHWC channels of a pixel (64 contiguous bytes for BF16); without pooling neighbouring
+//     lanes first exchange a packed word, so that each stores both filters of one pixel row as one 4- or 8-byte
+//     word.  The drain runs underneath the MMAs of the other accumulator stage.
+// What bounds it: the shared-memory fill.  Every 64-channel chunk brings 9 x 16 KB of filter taps and a 20 KB halo box
+// into each CTA for 128 x 224 x 576 multiply-adds, which at the full tensor rate is more than the L2 delivers to 148 SMs;
+// tensor memory (512 columns, half of them draining) caps the pixels one filter load serves at 224.
 // Barrier protocol, bounded waits and the final cluster barrier are those of direct_tc2.cu.
 #include <cstdlib>
 #include <mutex>

@@ -18,9 +18,13 @@
 //     the ring-slot and accumulator barriers of BOTH CTAs (tcgen05.commit ... multicast::cluster, an mbarrier signal);
 //   * warps 2-5 of each CTA: epilogue of that CTA's 128 accumulator lanes, as in gemm_tc.cu: tcgen05.ld 32 columns,
 //     128-byte-swizzled 32 x 32 float staging tile, TMA store (rows past the tile count and columns past Kq clipped).
+//     With M24 the products leave in 3 bytes each: 64 columns at a time, rounded to their upper 24 bits, as a
+//     128-byte-swizzled 64 x 32 tile of 16-bit upper halves and a 64-byte-swizzled tile of third bytes, two TMA stores
+//     into two planes of the product buffer (output_transform.cu reads them back).
 // Every mbarrier wait is bounded; a wait that gives up raises its CTA's abort flag, records a code, and both CTAs meet
 // at the final cluster barrier (the partner's waits run out too) before tensor memory is released.
-// Bound: the FP32 product write (a*a*T*Kq*4 bytes) against 2*a*a*T*C*K flops: HBM up to 512 channels, tensor pipe above.
+// Bound: the product write (a*a*T*Kq*4 bytes, 3 with M24) against 2*a*a*T*C*K flops, and the operand fill: at 512
+// channels the pair pulls 2 x 256 KB out of the L2 per work unit, 7 TB/s over the chip at the measured speed.
 #include <cstdlib>
 #include <mutex>
 

@@ -13,6 +13,8 @@
 //     contiguous along w;
 //   * CHWN: one tile position x 8 images x 32 filters are staged and written contiguous along n.
 // HBM bound: reads a*a*T*K floats, writes N*K*OH*OW elements (a quarter of that with the pool).
+// The NHWC kernel also reads products stored in 3 bytes (a plane of 16-bit upper halves and a plane of third bytes,
+// written by the CTA-pair tile GEMM): one 4-byte and one 2-byte load and two prmt per pair of products.
 #include <type_traits>
 
 #include "common.cuh"
