@@ -488,7 +488,8 @@ def run_ours(args, rank, world, local_rank):
             # Images are independent, so sharding must not change a single bit: the gathered result has to equal the same
             # shards run one after the other on this GPU alone.  The whole batch as ONE 256-image run is compared too; it may
             # differ in rounding where the engine picks another kernel for another batch size (512 channels at 28 x 28:
-            # direct kernel below 128 images, Winograd from there on), so that comparison also reports the relative L2 distance.
+            # direct kernel for a handful of images, Winograd otherwise; float or 3-byte products by the number of tile
+            # rows), so that comparison also reports the relative L2 distance.
             pieces = []
             for r in range(world):
                 lo_r, hi_r = shard.shard_range(global_batch, world, r)

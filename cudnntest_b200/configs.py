@@ -55,7 +55,7 @@ def engine_runs_winograd(dtype, layout, n, c, k, s, wino):
     if wino or dtype in ("fp32", "fp32x3"):
         return True
     if dtype == "bf16":
-        return not (c <= 256 or s * s < 28 * 28 or n * s * s < 128 * 28 * 28)
+        return not (c <= 256 or s * s < 28 * 28 or n * s * s < 4 * 28 * 28 or layout == "NCHW")
     return c > 256      # tf32
 
 

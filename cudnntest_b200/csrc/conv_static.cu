@@ -71,7 +71,10 @@ int wino_conv_forward_static(const wino_conv_desc* d, const void* x, const void*
     if ((rc = check_device())) return rc;
     if (direct_small_c_applies(*d)) return launch_direct_small_c(*d, g, x, u, bias, y, (cudaStream_t)stream);   // needs no scratch
     if (direct_tc_applies(*d)) return launch_direct_tc(*d, g, x, direct_filters(*d, g, u), bias, y, (cudaStream_t)stream);   // needs no scratch
-    if (direct_via_nhwc_applies(*d)) {      // NHWC staging of the whole batch has to fit the array
+    // NHWC staging of the whole batch has to fit the array; shapes whose filter buffer holds both forms fall back to
+    // the Winograd pipeline (slabs) when it does not
+    if (direct_via_nhwc_applies(*d) &&
+        !(direct_filter_mode(*d) == 2 && direct_via_nhwc_staging_bytes(*d, g) > kStaticScratchBytes)) {
         const size_t need = direct_via_nhwc_staging_bytes(*d, g);
         if (need > kStaticScratchBytes)
             return fail(WINO_E_WORKSPACE,

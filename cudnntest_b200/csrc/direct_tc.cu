@@ -301,9 +301,11 @@ int direct_tc_mode(const wino_conv_desc& d) {
     if (mode == 0) return 0;
     // WINO_DIRECT_TC_MAXC forces the channel limit; by default the choice follows what was measured on B200 (batch 256):
     // up to 256 input channels the direct kernel beats the three-kernel Winograd pipeline (whose transform-domain
-    // buffers are HBM-bound); at 512 channels Winograd's 4x fewer multiplies win, except on small images
-    // (14 x 14) and small batches (fewer than 128 images of 28 x 28) where its tile GEMMs are too small to fill the
-    // machine (512 -> 512 at 28 x 28, direct / Winograd: batch 64 0.162 / 0.179 ms, 128 0.319 / 0.317, 256 0.636 / 0.61).
+    // buffers are HBM-bound); at 512 channels Winograd's 4x fewer multiplies win, except on small images (14 x 14), on
+    // a handful of images (fewer than 4 x 28 x 28 pixels in the batch), and where NCHW is involved.  512 -> 512 at 28 x 28,
+    // direct / Winograd in microseconds: NHWC batch 4 27 / 18, 32 87 / 78, 64 161 / 145, 128 279 / 277 (float products;
+    // 3-byte products from there on), 256 620 / 555; NCHW (x staged to NHWC, y stored NCHW by the direct kernel) batch 32
+    // 95 / 128, 256 709 / 1060; CHWN batch 32 108 / 93, 256 752 / 688.
     static const int max_c = [] { const char* e = getenv("WINO_DIRECT_TC_MAXC"); return (e && *e) ? atoi(e) : -1; }();
     if (!(d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC && d.wino == 0) || out_type_differs(d)) return 0;
     if (d.dtype == WINO_TF32) {
@@ -317,9 +319,11 @@ int direct_tc_mode(const wino_conv_desc& d) {
     return (d.c <= 256 || (long long)d.h * d.w < 28 * 28) ? 1 : 2;
 }
 
+static bool handful_of_images(const wino_conv_desc& d) { return (long long)d.n * d.h * d.w < 4LL * 28 * 28; }
+
 bool direct_tc_applies(const wino_conv_desc& d) {
     const int mode = direct_tc_mode(d);
-    return mode == 1 || (mode == 2 && (long long)d.n * d.h * d.w < 128LL * 28 * 28);
+    return mode == 1 || (mode == 2 && handful_of_images(d));
 }
 
 size_t direct_tc_filter_bytes(const wino_conv_desc& d) { return (size_t)9 * d.k * d.c * (d.dtype == WINO_BF16 ? 2 : 4); }
@@ -335,7 +339,12 @@ static bool via_nhwc_enabled(const wino_conv_desc& d) {
     return !off && !(d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC);
 }
 
-bool direct_via_nhwc_applies(const wino_conv_desc& d) { return via_nhwc_enabled(d) && direct_tc_applies(nhwc_twin(d)); }
+bool direct_via_nhwc_applies(const wino_conv_desc& d) {
+    if (!via_nhwc_enabled(d)) return false;
+    const int mode = direct_tc_mode(nhwc_twin(d));
+    // batch-dependent shapes: with NCHW on either side the staged direct kernel wins at every batch (see direct_tc_mode)
+    return mode == 1 || (mode == 2 && (d.layout_in == WINO_NCHW || d.layout_out == WINO_NCHW || handful_of_images(d)));
+}
 
 int direct_filter_mode(const wino_conv_desc& d) {
     if (d.layout_in == WINO_NHWC && d.layout_out == WINO_NHWC) return direct_tc_mode(d);

@@ -48,7 +48,7 @@ def winograd_gemm_flops_per_image(wino=4, layers=VGG16_CONV):
 def kernel_model(batch, dtype="bf16", wino=4, layers=VGG16_CONV, layout="NHWC", forced_wino=False):
     """Algorithmic bytes and flops of one forward pass per kernel class, following the engine's per-layer choice
     for NHWC: C <= 3 (no pool): thin-input direct kernel; BF16 with C a multiple of 64 and (C <= 256, an image
-    smaller than 28 x 28 or fewer than 128 * 784 pixels in the batch): direct tensor-core kernel; other tensor-core layers with C <= 128: row-fused tile GEMM
+    smaller than 28 x 28, fewer than 4 * 784 pixels in the batch, or NCHW tensors): direct tensor-core kernel; other tensor-core layers with C <= 128: row-fused tile GEMM
     (products Z, a*m planes, half for bf16); otherwise the plain tile GEMM (products M, a*a planes of floats, or of 3-byte values where the CTA-pair kernel
     writes them for an NHWC result)."""
     a, m = wino + 2, wino
@@ -62,7 +62,7 @@ def kernel_model(batch, dtype="bf16", wino=4, layers=VGG16_CONV, layout="NHWC", 
             out["direct_thin_input"]["flops"] += batch * 2 * k * c * s * s * 9
             continue
         direct = (dtype == "bf16" and c % 64 == 0 and k % 8 == 0 and
-                  (c <= 256 or s * s < 28 * 28 or batch * s * s < 128 * 28 * 28)) or \
+                  (c <= 256 or s * s < 28 * 28 or batch * s * s < 4 * 28 * 28 or layout == "NCHW")) or \
                  (dtype == "tf32" and c % 32 == 0 and c <= 256 and k % 16 == 0 and k >= 64)
         if direct and not forced_wino:      # other layouts reach the same kernel through NHWC staging
             out["direct_tensor_core"]["bytes"] += batch * (c * s * s + k * o * o) * s_io

@@ -65,7 +65,7 @@ typedef struct wino_conv_desc {
     int wino;                  /* output tile size m of F(m x m, 3x3): 2 or 4.  0 = the engine chooses per shape:
                                   F(4x4,3x3), or a direct implicit-GEMM tensor-core kernel where that is faster
                                   (C <= 3; BF16 with C a multiple of 64, TF32 with C a multiple of 32, up to 256
-                                  channels, and wider BF16 layers on small images or small batches; NCHW / CHWN
+                                  channels, and wider BF16 layers on small images, a handful of images or NCHW tensors; NCHW / CHWN
                                   reach it through NHWC staging in the caller's scratch)                  */
     int relu, has_bias, pool2x2; /* epilogue fused into the output transform: y = pool(relu(conv+b)) */
     int slab_images;           /* images transformed per pass; 0 = as many as fit a 2 GiB scratch       */

@@ -81,7 +81,7 @@ def test_buffer_sizes(L, shape, dtype, m):
 def test_filter_buffer_does_not_depend_on_the_batch(L, layout, dtype, chw):
     """Weights are transformed once and used with any batch size: the size (and with it the format) of the filter
     buffer must not change with n, although the engine's kernel choice does (512 channels at 28 x 28: direct kernel
-    below 128 images, Winograd from there on, so that buffer holds both forms)."""
+    for fewer than 4 images, Winograd from there on, so that buffer holds both forms)."""
     c, h, w, k = chw
     sizes = {L.wino_filter_bytes(ctypes.byref(cb.make_desc(n, c, h, w, k, layout=layout, dtype=dtype))) for n in (1, 8, 127, 128, 256)}
     assert len(sizes) == 1 and 0 not in sizes

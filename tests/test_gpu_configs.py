@@ -114,8 +114,8 @@ def test_cross_layout_tensor_core(cb, dtype, shape, pool):
 
 @pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
 def test_filters_transformed_once_serve_every_batch_size(cb, layout):
-    """512 -> 512 at 28 x 28, BF16: the engine runs the direct kernel below 128 images and the Winograd pipeline from
-    there on.  One filter buffer, written through a descriptor of either batch size, serves both."""
+    """512 -> 512 at 28 x 28, BF16: in NHWC the engine runs the direct kernel for fewer than 4 images and the Winograd
+    pipeline from there on (in NCHW the staged direct kernel at every batch).  One filter buffer, written through a descriptor of either batch size, serves both."""
     import torch
     c, h, k = 512, 28, 512
     x, wt, b = make_inputs(130, c, h, h, k, seed=0xC0DE0021)
