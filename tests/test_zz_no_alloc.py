@@ -99,3 +99,19 @@ def test_static_scratch_rejects_oversized_problem():
     msg = L.wino_last_error_string().decode()
     assert "built-in array holds" in msg and "67108864" in msg
     assert L.wino_device_status() == 0
+
+
+def test_static_scratch_falls_back_to_slabs_when_the_staging_does_not_fit():
+    """BF16 NCHW, 512 channels at 28 x 28: the engine takes the staged direct kernel at every batch, and the filter buffer
+    of such a shape holds the Winograd form too.  96 images need 77 MB of NHWC staging, more than the built-in array: the
+    allocation-free entry then walks the batch in Winograd slabs instead of refusing.  Different kernels, so the two
+    results agree to the BF16 tolerance, not bit for bit."""
+    import torch
+    assert torch.cuda.is_available()
+    import cudnntest_b200 as cb
+    from util import rel_l2
+    ref, outs = _run_both(cb, 96, 512, 28, 28, 64, "NCHW", "bf16", seed=96 + 512 + 64, wino=0, slab_images=0)
+    for y in outs:
+        assert np.isfinite(y).all()
+        assert rel_l2(y, ref.astype(np.float64)) <= 5e-3
+    assert np.array_equal(outs[0], outs[1])
