@@ -86,14 +86,22 @@ __device__ __forceinline__ void store_row_nchw(void* y, long long off, const flo
     }
 }
 
-template <int TH, int A_STAGES, int B_STAGES>
+// FLATW = 0: a pixel tile is 8 columns x TH rows of the image and the halo box 10 x (TH + 2) pixels.
+// FLATW > 0 (images exactly FLATW - 2 pixels wide): a tile is TH whole image rows.  The halo box is FLATW x (TH + 2)
+// pixels, and the MMA's pixel index runs over the box row after row: index j = row * FLATW + column, tap (dy, dx) reads
+// pixel j + dy * FLATW + dx, which is a plain shift of the start address.  The two indices per row that fall on the halo
+// columns are computed and dropped.  28-wide images lose 6.7 % of the MMA columns that way instead of the 12.5 % of
+// four 8-wide tiles, and a filter tap loaded from the L2 serves 224 real pixels of a pair instead of 196.
+template <int TH, int A_STAGES, int B_STAGES, int FLATW = 0>
 struct DttSmem {
-    static constexpr int PX_BYTES = DT_BOX_W * (TH + 2) * 128;                 // bytes one halo box brings in
-    static constexpr int PX_STRIDE = (PX_BYTES + 1023) / 1024 * 1024;
+    static constexpr int BOX_W = FLATW ? FLATW : DT_BOX_W;
+    static constexpr int PX_BYTES = BOX_W * (TH + 2) * 128;                    // bytes one halo box brings in
+    // (the last taps of a flat tile read two pixels past the box: they only feed dropped columns, and stay inside the slot)
+    static constexpr int PX_STRIDE = (PX_BYTES + 256 + 1023) / 1024 * 1024;
     static constexpr int A_OFF = 0;                                            // pixel boxes
     static constexpr int B_OFF = A_OFF + A_STAGES * PX_STRIDE;                 // filter taps
     static constexpr int BAR_OFF = B_OFF + B_STAGES * DTT_W_TILE;
-    static constexpr int NPIX = DT_TW * TH;                                    // pixel columns per CTA
+    static constexpr int NPIX = FLATW ? FLATW * TH : DT_TW * TH;               // pixel columns per CTA
     static constexpr int NCOL = 2 * NPIX;                                      // MMA N: both CTAs' pixels
     static constexpr int ACC = 512 / NCOL < 4 ? 512 / NCOL : 4;
     static constexpr int NBARS = 2 * A_STAGES + 2 * B_STAGES + 2 * ACC;
@@ -101,11 +109,12 @@ struct DttSmem {
     static constexpr int TOTAL = SLOT_OFF + 16 + 1024;
 };
 
-template <int TH, int A_STAGES, int B_STAGES, bool TF32>
+template <int TH, int A_STAGES, int B_STAGES, bool TF32, int FLATW = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(DT_THREADS, 1)
 direct_tc2t_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const DtParams p) {
-    using L = DttSmem<TH, A_STAGES, B_STAGES>;
-    static_assert(TH % 2 == 0 && TH >= 8 && TH <= 16, "pixel tile height");
+    using L = DttSmem<TH, A_STAGES, B_STAGES, FLATW>;
+    static_assert(FLATW ? (TH == 4 && FLATW == 30) : (TH % 2 == 0 && TH >= 8 && TH <= 16), "pixel tile shape");
+    static_assert(L::NPIX % 8 == 0 && L::NPIX <= 128, "pixel columns per CTA");
     static_assert(L::ACC >= 2, "accumulators are at least double-buffered");
     constexpr int ACC = L::ACC, NPIX = L::NPIX, NCOL = L::NCOL;
     constexpr int CPC = TF32 ? 32 : 64;      // channels per 128-byte chunk
@@ -197,14 +206,15 @@ direct_tc2t_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                     const int st = (int)(acount % A_STAGES);
                     if (!mbar_wait_warp(bar_afull + 8 * st, (uint32_t)((acount / A_STAGES) & 1), abort_flag, p.status, DT_W_A_FULL)) { ok = false; break; }
                     tc_fence_after();
-                    const uint64_t px_desc0 = smem_desc_k128_sbo(base + L::A_OFF + st * L::PX_STRIDE, DT_BOX_W * 128);
+                    // 8-pixel groups of the N operand: one tile row (next group = next halo row), or consecutive pixels of the box
+                    const uint64_t px_desc0 = smem_desc_k128_sbo(base + L::A_OFF + st * L::PX_STRIDE, FLATW ? 1024 : DT_BOX_W * 128);
 #pragma unroll
                     for (int tap = 0; tap < 9; ++tap) {
                         const int sb = (int)(bcount % B_STAGES);
                         if (!mbar_wait_warp(bar_bfull + 8 * sb, (uint32_t)((bcount / B_STAGES) & 1), abort_flag, p.status, DT_W_B_FULL)) { ok = false; break; }
                         tc_fence_after();
                         const uint64_t w_desc = smem_desc_k128(base + L::B_OFF + sb * DTT_W_TILE);
-                        const uint64_t px_desc = px_desc0 + (uint64_t)((((tap / 3) * DT_BOX_W + (tap % 3)) * 128) >> 4);
+                        const uint64_t px_desc = px_desc0 + (uint64_t)((((tap / 3) * L::BOX_W + (tap % 3)) * 128) >> 4);
 #pragma unroll
                         for (int ks = 0; ks < 4; ++ks) {
                             if (tap == 0 && ks == 0)
@@ -241,30 +251,19 @@ direct_tc2t_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             const bool k_ok = valid && kch < p.K;
             const float bias = (p.bias && kch < p.K) ? __ldg(p.bias + kch) : 0.f;
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * NCOL) + who * NPIX;
-            const int oy0 = ty * TH, ox0 = tx * DT_TW;
+            const int oy0 = ty * TH;
             // lanes 2j and 2j+1 hold neighbouring filters: in the unpooled NHWC store the even lane takes the upper pixel
             // row of a step for both filters and the odd lane the lower one, so that every store is one 4- or 8-byte word
             const int odd = lane & 1;
-            const int nvalid = min(8, p.OW - ox0);
-            uint32_t r[16];
-            tmem_ld_32x16(lane_addr, r);
-#pragma unroll 1
-            for (int pr = 0; pr < TH / 2; ++pr) {     // two pixel rows (16 columns) per step: one row of 2x2 pool windows
-                tmem_ld_wait();
-                float v[16];
+            // bias, ReLU, pool and store of 8 pixels x 2 rows of this thread's filter: v[e] = (row oy, column ox0 + e),
+            // v[8 + e] = (row oy + 1, column ox0 + e)
+            auto emit = [&](float (&v)[16], int oy, int ox0) {
+                const int nvalid = min(8, p.OW - ox0);
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
-                    v[e] = __uint_as_float(r[e]) + bias;
+                    v[e] += bias;
                     if (p.relu) v[e] = fmaxf(v[e], 0.f);
                 }
-                if (pr == TH / 2 - 1) {               // accumulator stage drained: release it on the leader
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * as);
-                } else {
-                    tmem_ld_32x16(lane_addr + (pr + 1) * 16, r);    // in flight while this step's values leave
-                }
-                const int oy = oy0 + 2 * pr;
                 if (p.y_nchw) {
                     // NCHW: this thread's filter is a plane of y and its registers are runs of consecutive pixels of a row
                     // (8 outputs, or 4 pooled ones): they leave as the widest vectors the row pitch keeps aligned
@@ -325,6 +324,55 @@ direct_tc2t_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                         }
                     }
                 }
+            };
+            if constexpr (FLATW != 0) {
+                // TH = 4 rows of FLATW = 30 columns: a pair of rows is 60 consecutive accumulator columns, read as 64 from a
+                // multiple of 8 (0 for rows 0-1, 56 for rows 2-3: their first column is then register 4)
+#pragma unroll
+                for (int rp = 0; rp < 2; ++rp) {
+                    constexpr int OW_ = FLATW - 2;
+                    uint32_t r[64];
+                    tmem_ld_32x32(lane_addr + rp * 56, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+                    tmem_ld_32x32(lane_addr + rp * 56 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+                    tmem_ld_wait();
+                    if (rp == 1) {                        // accumulator stage drained: release it on the leader
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * as);
+                    }
+                    const int off = rp * 4;
+#pragma unroll
+                    for (int c0 = 0; c0 < OW_; c0 += 8) {
+                        float v[16];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            // columns past the image (the last group has 4) are never stored: any register will do
+                            const int c = c0 + e < OW_ ? c0 + e : OW_ - 1;
+                            v[e] = __uint_as_float(r[off + c]);
+                            v[8 + e] = __uint_as_float(r[off + FLATW + c]);
+                        }
+                        emit(v, oy0 + 2 * rp, c0);
+                    }
+                }
+            } else {
+                const int ox0 = tx * DT_TW;
+                uint32_t r[16];
+                tmem_ld_32x16(lane_addr, r);
+#pragma unroll 1
+                for (int pr = 0; pr < TH / 2; ++pr) {     // two pixel rows (16 columns) per step: one row of 2x2 pool windows
+                    tmem_ld_wait();
+                    float v[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(r[e]);
+                    if (pr == TH / 2 - 1) {               // accumulator stage drained: release it on the leader
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * as);
+                    } else {
+                        tmem_ld_32x16(lane_addr + (pr + 1) * 16, r);    // in flight while this step's values leave
+                    }
+                    emit(v, oy0 + 2 * pr, ox0);
+                }
             }
             if (++as == ACC) { as = 0; aphase ^= 1; }
         }
@@ -340,16 +388,16 @@ direct_tc2t_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     }
 }
 
-template <int TH, int A_STAGES, int B_STAGES, bool TF32>
+template <int TH, int A_STAGES, int B_STAGES, bool TF32, int FLATW = 0>
 int run_t(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const DtParams& p, cudaStream_t st) {
-    using L = DttSmem<TH, A_STAGES, B_STAGES>;
+    using L = DttSmem<TH, A_STAGES, B_STAGES, FLATW>;
     static_assert(L::TOTAL <= 232448, "shared memory budget of one CTA exceeded");
     static std::once_flag once[64];
     int dev = 0;
     WINO_CUDA_CHECK(cudaGetDevice(&dev));
     cudaError_t attr_err = cudaSuccess;
     std::call_once(once[dev & 63], [&] {
-        attr_err = cudaFuncSetAttribute(direct_tc2t_kernel<TH, A_STAGES, B_STAGES, TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        attr_err = cudaFuncSetAttribute(direct_tc2t_kernel<TH, A_STAGES, B_STAGES, TF32, FLATW>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     });
     WINO_CUDA_CHECK(attr_err);
     const long long total_tiles = (long long)p.N * p.tiles_x * p.tiles_y;
@@ -359,7 +407,7 @@ int run_t(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const DtParams& p, c
     if (pairs < 1) pairs = 1;
     ProfScope prof(STAGE_DIRECT_TC, st);
     count_launch();
-    WINO_CUDA_CHECK(launch_kernel(direct_tc2t_kernel<TH, A_STAGES, B_STAGES, TF32>, dim3((unsigned)(2 * pairs)), dim3(DT_THREADS), L::TOTAL, st,
+    WINO_CUDA_CHECK(launch_kernel(direct_tc2t_kernel<TH, A_STAGES, B_STAGES, TF32, FLATW>, dim3((unsigned)(2 * pairs)), dim3(DT_THREADS), L::TOTAL, st,
                                   pdl_enabled(), tm_x, tm_w, p));
     WINO_CUDA_CHECK(cudaGetLastError());
     return WINO_OK;
@@ -395,15 +443,19 @@ int launch_direct_tc2t(const wino_conv_desc& d, const Geometry& g, const void* x
         return fail(WINO_E_BADARG, "direct conv: buffers (and the bias) must be 16-byte aligned");
     const bool tf32 = d.dtype == WINO_TF32;
     const int es = tf32 ? 4 : 2;
-    const int th = pick_tile_height(g.oh);
+    // 28-wide images: tiles of 4 whole rows over the flattened halo box (see DttSmem); WINO_DIRECT_FLAT=0 keeps the 8-wide tiles
+    static const bool flat_off = [] { const char* e = getenv("WINO_DIRECT_FLAT"); return e && e[0] == '0'; }();
+    const bool flat = !flat_off && g.ow == 28;
+    const int th = flat ? 4 : pick_tile_height(g.oh);
+    const int box_w = flat ? 30 : DT_BOX_W, npix = flat ? 30 * 4 : DT_TW * th;
     DtParams p;
     p.bias = d.has_bias ? bias : nullptr; p.y = y;
     p.N = d.n; p.OH = g.oh; p.OW = g.ow; p.K = d.k; p.pad = d.pad; p.PH = g.ph; p.PW = g.pw;
-    p.tiles_x = (g.ow + DT_TW - 1) / DT_TW; p.tiles_y = (g.oh + th - 1) / th;
+    p.tiles_x = flat ? 1 : (g.ow + DT_TW - 1) / DT_TW; p.tiles_y = (g.oh + th - 1) / th;
     p.cchunks = d.c / (128 / es);
     p.relu = d.relu; p.pool = d.pool2x2; p.y_nchw = y_nchw ? 1 : 0;
     p.nblocks = (d.k + 255) / 256;
-    p.idesc = make_idesc(tf32 ? OP_TF32 : OP_BF16, 2 * DT_TW * th, 256);
+    p.idesc = make_idesc(tf32 ? OP_TF32 : OP_BF16, 2 * npix, 256);
     int rc = status_word(&p.status);
     if (rc) return rc;
     CUtensorMap tm_x, tm_w;
@@ -411,10 +463,11 @@ int launch_direct_tc2t(const wino_conv_desc& d, const Geometry& g, const void* x
         const unsigned long long ues = (unsigned long long)es;
         const unsigned long long dims[4] = {(unsigned long long)d.c, (unsigned long long)d.w, (unsigned long long)d.h, (unsigned long long)d.n};
         const unsigned long long strides[3] = {d.c * ues, (unsigned long long)d.w * d.c * ues, (unsigned long long)d.h * d.w * d.c * ues};
-        const unsigned box[4] = {(unsigned)(128 / es), (unsigned)DT_BOX_W, (unsigned)(th + 2), 1u};
+        const unsigned box[4] = {(unsigned)(128 / es), (unsigned)box_w, (unsigned)(th + 2), 1u};
         if ((rc = encode_tensor_map(&tm_x, tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, x, dims, strides, box, true))) return rc;
     }
     if ((rc = make_map_k128(&tm_w, tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, es, packed, d.c, d.k, d.k, 9, 128))) return rc;
+    if (flat) return tf32 ? run_t<4, 4, 8, true, 30>(tm_x, tm_w, p, st) : run_t<4, 4, 8, false, 30>(tm_x, tm_w, p, st);
     switch (th) {
         case 16: return run_th<16>(tf32, tm_x, tm_w, p, st);
         case 14: return run_th<14>(tf32, tm_x, tm_w, p, st);

@@ -93,6 +93,7 @@ def test_vgg16_stack_batch256_routing(cb):
 @pytest.mark.parametrize("shape,pool", [((3, 64, 18, 14, 96), False), ((3, 64, 18, 14, 96), True),      # direct kernel + staging
                                         ((2, 64, 18, 14, 256), False), ((2, 64, 18, 14, 256), True),    # filters-as-M kernel: NCHW stored in place, odd row pitches
                                         ((1, 64, 12, 28, 256), False), ((1, 64, 6, 40, 384), True),     # ... 8-byte and 16-byte vectors, clipped tiles
+                                        ((1, 64, 14, 28, 256), True),                                   # ... flattened-row tiles with the pool
                                         ((2, 328, 14, 10, 72), False), ((2, 328, 14, 10, 72), True)])   # Winograd route
 def test_cross_layout_tensor_core(cb, dtype, shape, pool):
     """All nine (source, destination) pairs: each result against the oracle, and the same numbers whatever the

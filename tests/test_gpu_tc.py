@@ -151,7 +151,9 @@ def test_thin_input_direct_path(cb, dtype, layout, shape):
                                         ((1, 512, 14, 14, 512), True), ((3, 256, 12, 20, 144), True), ((1, 320, 6, 6, 96), False),
                                         ((5, 64, 40, 24, 128), True), ((1, 64, 8, 16, 64), False), ((3, 64, 30, 20, 384), True),
                                         ((1, 128, 7, 9, 256), False), ((2, 64, 22, 16, 256), True), ((1, 64, 10, 8, 256), False),
-                                        ((2, 64, 19, 21, 128), False), ((1, 64, 13, 10, 144), False)])
+                                        ((2, 64, 19, 21, 128), False), ((1, 64, 13, 10, 144), False),
+                                        # 28-wide outputs: tiles of 4 whole rows over the flattened halo box (a partial last tile; pad 0)
+                                        ((2, 64, 28, 28, 256), False), ((1, 128, 27, 28, 512), True), ((1, 64, 30, 30, 256), False)])
 def test_direct_tensor_core_path(cb, shape, pool):
     """NHWC BF16 layers with C a multiple of 64 and no explicit tile size run the implicit-GEMM kernels (halo box +
     shifted descriptors; CTA pairs when K is a multiple of 16, the single-CTA kernel otherwise): against the oracle,
@@ -174,7 +176,7 @@ def test_direct_tensor_core_path(cb, shape, pool):
 
 @pytest.mark.parametrize("shape,pool", [((2, 64, 32, 24, 64), True), ((1, 128, 20, 20, 128), False), ((3, 32, 17, 13, 80), True),
                                         ((2, 256, 16, 24, 256), True), ((1, 96, 9, 9, 64), False), ((1, 64, 12, 12, 512), False),
-                                        ((1, 64, 7, 9, 256), False)])
+                                        ((1, 64, 7, 9, 256), False), ((1, 64, 14, 28, 256), True)])
 @pytest.mark.parametrize("layout", ["NHWC", "NCHW", "CHWN"])
 def test_direct_tensor_core_path_tf32(cb, shape, pool, layout):
     """Float storage with TF32 operands: C a multiple of 32 (up to 256) and K a multiple of 16 run the CTA-pair
